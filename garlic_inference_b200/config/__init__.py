@@ -1,4 +1,6 @@
 from .base import (ConfigError, LayerSpec, ModelPlan, PartSpec, ScheduleEntry)
+from .dugopel import ARCHITECTURE as DUGOPEL_ARCHITECTURE
+from .dugopel import DugopelConfig
 from .fivitar import ARCHITECTURE as FIVITAR_ARCHITECTURE
 from .fivitar import FivitarConfig
 from .qwen3 import ARCHITECTURE as QWEN3_ARCHITECTURE
@@ -11,6 +13,7 @@ from .registry import (architecture_name, config_class_for, known_architectures,
 register_architecture(QWEN3_ARCHITECTURE, Qwen3Config)
 register_architecture(FIVITAR_ARCHITECTURE, FivitarConfig)
 register_architecture(ZOGULORN_ARCHITECTURE, ZogulornConfig)
+register_architecture(DUGOPEL_ARCHITECTURE, DugopelConfig)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "Qwen3Config", "FivitarConfig", "ZogulornConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "Qwen3Config", "FivitarConfig", "ZogulornConfig", "DugopelConfig",
            "architecture_name", "config_class_for", "known_architectures", "load_config", "register_architecture"]

@@ -8,15 +8,30 @@
 // themselves gives sum_j p_j c_j, and W_uv,h is applied to that afterwards: the cache is read once for all
 // heads and keys and values are never expanded.
 //
-// Rotation: pair (2i, 2i+1) of the rotated part, i < n_rot / 2, turns by the float32 product
-// position * freq[i]; cosine and sine are multiplied by `magnitude`; dimensions from n_rot on pass.
+// Rotation: pair (2i, 2i+1) of the rotated part (or, in the half layout, pair (i, i + n_rot/2)), i < n_rot / 2,
+// turns by the float32 product position * freq[i]; cosine and sine are multiplied by `magnitude`; dimensions from
+// n_rot on pass.  The queries may come from a matrix of their own (an up-projection behind a normed latent), and a
+// layer that reads another layer's cache rows brings no latent to append (kv_src = null).
 // NikolayBlagoev/garlic-inference has one attention (grouped-query, src/models/qwen3/qwen3.cpp:140-179) and
 // the rotate-half layout (src/src-cuda/rope.cu:41-79).
 #include "common.cuh"
 #include <math.h>
 
+// Element j < n_rot of a rotated part `x` after the turn (cs, sn: the pairs' cosines and sines).
 template <typename T>
-__global__ void latent_prepare_kernel(const T* __restrict__ proj, long long ld, int q_off, int c_off,
+__device__ __forceinline__ float turned(const T* x, int j, int n_rot, int half, const float* cs, const float* sn) {
+    if (half) {
+        const int h = n_rot >> 1;
+        return j < h ? to_f32(x[j]) * cs[j] - to_f32(x[j + h]) * sn[j]
+                     : to_f32(x[j]) * cs[j - h] + to_f32(x[j - h]) * sn[j - h];
+    }
+    const float a = to_f32(x[j & ~1]), b = to_f32(x[j | 1]);
+    return (j & 1) ? b * cs[j >> 1] + a * sn[j >> 1] : a * cs[j >> 1] - b * sn[j >> 1];
+}
+
+template <typename T>
+__global__ void latent_prepare_kernel(const T* __restrict__ q_src, long long ldq, int q_off,
+                                      const T* __restrict__ kv_src, long long ld, int c_off, int half,
                                       const T* __restrict__ q_lat, const void* __restrict__ norm_w, int w_dtype,
                                       float eps, const float* __restrict__ freq, float magnitude, int n_rot,
                                       const int* __restrict__ tok_pos, const int* __restrict__ tok_slot,
@@ -29,7 +44,6 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, long long ld, 
     __shared__ float cs_s[128], sn_s[128];             // cosine and sine of the token's angles, pairs 0 .. n_rot/2 - 1
     const int t = blockIdx.x, part = blockIdx.y;       // part < H: that head's query row; part == H: the cache row
     const int pos = tok_pos[t], slot = tok_slot[t];
-    const T* row = proj + (size_t)t * ld;
     const float p = (float)pos;
     for (int i = threadIdx.x; i < n_rot / 2; i += blockDim.x) {
         float sn, cs;
@@ -40,7 +54,7 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, long long ld, 
 
     if (part < H) {                                    // queries: [ q' (rank) | rotated part (dr) | zeros ]
         const int h = part;
-        const T* qr = row + q_off + (size_t)h * (d + dr) + d;
+        const T* qr = q_src + (size_t)t * ldq + q_off + (size_t)h * (d + dr) + d;
         const T* ql = q_lat + ((size_t)t * H + h) * rank;
         T* dst = q_out + ((size_t)t * H + h) * row_w;
 #pragma unroll 4
@@ -50,25 +64,20 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, long long ld, 
                 v = to_f32(ql[c]);
             } else if (c < rank + dr) {
                 const int j = c - rank;
-                if (j < n_rot) {
-                    const float a = to_f32(qr[j & ~1]), b = to_f32(qr[j | 1]);
-                    v = (j & 1) ? b * cs_s[j >> 1] + a * sn_s[j >> 1] : a * cs_s[j >> 1] - b * sn_s[j >> 1];
-                } else {
-                    v = to_f32(qr[j]);
-                }
+                v = j < n_rot ? turned(qr, j, n_rot, half, cs_s, sn_s) : to_f32(qr[j]);
             }
             dst[c] = from_f32<T>(v);
         }
         return;
     }
-    if (!append || slot < 0) return;
+    if (!append || slot < 0 || !kv_src) return;
     const int lp = pos / page_size;
     if (pos < 0 || lp >= max_pages) { if (threadIdx.x == 0) atomicExch(status, 1); return; }
     const int page = block_table[(size_t)slot * max_pages + lp];
     if (page < 0 || page >= n_pool_pages) { if (threadIdx.x == 0) atomicExch(status, 2); return; }
     T* dst = pool + ((size_t)page * page_size + (pos - lp * page_size)) * row_w;
 
-    const T* cr = row + c_off;
+    const T* cr = kv_src + (size_t)t * ld + c_off;
     float ss = 0.f;
 #pragma unroll 4
     for (int c = threadIdx.x; c < rank; c += blockDim.x) { const float x = to_f32(cr[c]); ss += x * x; }
@@ -82,18 +91,14 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, long long ld, 
         } else if (c < rank + dr) {
             const int j = c - rank;
             const T* kr = cr + rank;
-            if (j < n_rot) {
-                const float a = to_f32(kr[j & ~1]), b = to_f32(kr[j | 1]);
-                v = (j & 1) ? b * cs_s[j >> 1] + a * sn_s[j >> 1] : a * cs_s[j >> 1] - b * sn_s[j >> 1];
-            } else {
-                v = to_f32(kr[j]);
-            }
+            v = j < n_rot ? turned(kr, j, n_rot, half, cs_s, sn_s) : to_f32(kr[j]);
         }
         dst[c] = from_f32<T>(v);
     }
 }
 
-extern "C" int gi_latent_prepare(const void* proj, long long ld, int q_off, int c_off, const void* q_lat,
+extern "C" int gi_latent_prepare(const void* q_src, long long ldq, int q_off, const void* kv_src, long long ld, int c_off,
+                                 int half, const void* q_lat,
                                  int act_dtype, const void* norm_w, int w_dtype, float eps, const float* freq,
                                  float magnitude, int n_rot, const int* tok_pos, const int* tok_slot,
                                  const int* block_table, void* pool, void* q_out, int n_tokens, int H, int d, int dr,
@@ -104,15 +109,16 @@ extern "C" int gi_latent_prepare(const void* proj, long long ld, int q_off, int 
                row_w, rank, dr);
     GI_REQUIRE(n_rot % 2 == 0 && n_rot <= dr && n_rot <= 256, "gi_latent_prepare: %d rotated dimensions of %d (at most 256)", n_rot, dr);
     GI_REQUIRE(H < 65535, "gi_latent_prepare: %d heads", H);
+    GI_REQUIRE(kv_src || !append, "gi_latent_prepare: nothing to append without a latent of the layer's own");
     if (n_tokens == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32)
-        gi_launch(latent_prepare_kernel<float>, dim3(n_tokens, H + 1), dim3(128), 0, s, (const float*)proj, ld, q_off, c_off,
-                  (const float*)q_lat, norm_w, w_dtype, eps, freq, magnitude, n_rot, tok_pos, tok_slot, block_table,
+        gi_launch(latent_prepare_kernel<float>, dim3(n_tokens, H + 1), dim3(128), 0, s, (const float*)q_src, ldq, q_off,
+                  (const float*)kv_src, ld, c_off, half, (const float*)q_lat, norm_w, w_dtype, eps, freq, magnitude, n_rot, tok_pos, tok_slot, block_table,
                   (float*)pool, (float*)q_out, H, d, dr, rank, row_w, page_size, max_pages, n_pool_pages, append, status);
     else if (act_dtype == GI_DTYPE_BF16)
-        gi_launch(latent_prepare_kernel<bf16>, dim3(n_tokens, H + 1), dim3(128), 0, s, (const bf16*)proj, ld, q_off, c_off,
-                  (const bf16*)q_lat, norm_w, w_dtype, eps, freq, magnitude, n_rot, tok_pos, tok_slot, block_table,
+        gi_launch(latent_prepare_kernel<bf16>, dim3(n_tokens, H + 1), dim3(128), 0, s, (const bf16*)q_src, ldq, q_off,
+                  (const bf16*)kv_src, ld, c_off, half, (const bf16*)q_lat, norm_w, w_dtype, eps, freq, magnitude, n_rot, tok_pos, tok_slot, block_table,
                   (bf16*)pool, (bf16*)q_out, H, d, dr, rank, row_w, page_size, max_pages, n_pool_pages, append, status);
     else
         GI_REQUIRE(false, "gi_latent_prepare: activation dtype %d", act_dtype);

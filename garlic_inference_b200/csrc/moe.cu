@@ -4,7 +4,12 @@
 //   gi_router_logits   z = W_r x in float32 (float32 weight, the token's vector widened)
 //   gi_router_topk     per token: the `top` largest of its float32 router logits (ties: the lower index), in
 //                      falling order, and the softmax over those chosen logits alone
-//   gi_moe_up          a[t, j, :] = act( W_up[e_tj] x_t )          act: the square of relu (0) or silu (1)
+//   gi_router_select   per token: scores = softmax of its float32 router logits over all experts; the experts lie in
+//                      `groups` equal groups of neighbours, a group's score is its best expert's, and only the
+//                      `keep` best groups stay; the `top` largest scores among them are chosen (ties: the lower
+//                      index), in falling order; the weights are those scores times `scale`, not renormalised
+//   gi_moe_up          a[t, j, :] = act( W_up[e_tj] x_t )          act: the square of relu (0) or silu (1); or (2)
+//                      a gated unit: W_up[e] holds ff gate rows and then ff up rows, a = unit(gate, up) (glu.cuh)
 //   gi_moe_down        part[t, j, :] = W_down[e_tj] a[t, j, :]
 //   gi_moe_group       the (token, choice) pairs in the order of their experts: each pair's row, each expert's last
 //                      row, and the tokens' vectors gathered into that order (a stable counting sort)
@@ -18,6 +23,7 @@
 // fixed order; a token's result does not depend on the other tokens of the step.
 // NikolayBlagoev/garlic-inference's mixture-of-experts path is a different design (src/models/qwen3/qwen3-moe.cpp).
 #include "common.cuh"
+#include "glu.cuh"
 #include <math.h>
 
 // ------------------------------------------------------------------ router
@@ -64,6 +70,100 @@ extern "C" int gi_router_topk(const float* logits, long long ld, int E, int top,
     gi_launch(router_topk_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits, ld, E, top, idx_out,
               w_out, n_rows);
     return gi_check_launch("gi_router_topk");
+}
+
+// Scores over all experts, groups of neighbours, the best groups' best experts.  A warp per token; its scores and
+// its groups' scores live in shared memory.
+#define RS_WARPS 4
+__global__ void __launch_bounds__(RS_WARPS * 32)
+router_select_kernel(const float* __restrict__ logits, long long ld, int E, int top, int groups, int keep, float scale,
+                     int* __restrict__ idx_out, float* __restrict__ w_out, int n_rows) {
+    gi_pdl_start();
+    extern __shared__ float rs_smem[];                   // per warp: E scores, then `groups` group scores
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * RS_WARPS + warp;
+    if (r >= n_rows) return;
+    float* sc = rs_smem + (size_t)warp * (E + groups);
+    float* gs = sc + E;
+    const float* z = logits + (size_t)r * ld;
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - m); sc[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) sc[e] = sc[e] / sum;
+    __syncwarp();
+    const int per = E / groups;
+    if (keep < groups) {
+        for (int g = lane; g < groups; g += 32) {
+            float b = -INFINITY;
+            for (int k = 0; k < per; ++k) b = fmaxf(b, sc[g * per + k]);
+            gs[g] = b;
+        }
+        __syncwarp();
+        // the `keep` best groups in the order (score falling, index rising); the others' experts leave the choice
+        float prev_v = INFINITY;
+        int prev_i = -1;
+        for (int j = 0; j < keep; ++j) {
+            float best = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const float v = gs[g];
+                const bool after = v < prev_v || (v == prev_v && g > prev_i);
+                if (after && (v > best || (v == best && g < bi))) { best = v; bi = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+            }
+            prev_v = best; prev_i = bi;
+        }
+        __syncwarp();
+        // a group stays if it comes no later than the last one kept in that order
+        for (int g = lane; g < groups; g += 32) {
+            const float v = gs[g];
+            const bool kept = v > prev_v || (v == prev_v && g <= prev_i);
+            gs[g] = kept ? 1.f : 0.f;
+        }
+        __syncwarp();
+    }
+    float prev_v = INFINITY;
+    int prev_i = -1;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            if (keep < groups && gs[e / per] == 0.f) continue;
+            const float v = sc[e];
+            const bool after = v < prev_v || (v == prev_v && e > prev_i);
+            if (after && (v > best || (v == best && e < bi))) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) { idx_out[(size_t)r * top + j] = bi; w_out[(size_t)r * top + j] = best * scale; }
+        prev_v = best; prev_i = bi;
+    }
+}
+
+extern "C" int gi_router_select(const float* logits, long long ld, int E, int top, int groups, int keep, float scale,
+                                int* idx_out, float* w_out, int n_rows, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && E > 0 && ld >= E, "gi_router_select: sizes");
+    GI_REQUIRE(groups > 0 && E % groups == 0 && keep > 0 && keep <= groups, "gi_router_select: %d experts in %d groups of which %d stay", E, groups, keep);
+    GI_REQUIRE(top > 0 && top <= keep * (E / groups), "gi_router_select: %d of the %d experts that stay", top, keep * (E / groups));
+    const size_t smem = (size_t)RS_WARPS * (E + groups) * sizeof(float);
+    GI_REQUIRE(smem <= 48 * 1024, "gi_router_select: %d experts do not fit shared memory", E);
+    if (n_rows == 0) return 0;
+    gi_launch(router_select_kernel, dim3((n_rows + RS_WARPS - 1) / RS_WARPS), dim3(RS_WARPS * 32), smem, (cudaStream_t)stream,
+              logits, ld, E, top, groups, keep, scale, idx_out, w_out, n_rows);
+    return gi_check_launch("gi_router_select");
 }
 
 // ------------------------------------------------------------------ one row times a chosen expert's matrix
@@ -168,7 +268,7 @@ static int moe_rows_per_block(int pairs, int n_out) {
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_up_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w_up, const int* __restrict__ idx,
-              T* __restrict__ a, int top, int E, int ff, int hidden, int act, int rows_pb) {
+              T* __restrict__ a, int top, int E, int ff, int hidden, int act, int rows_pb, GluShape unit) {
     gi_pdl_start();
     extern __shared__ float xs[];                   // hidden
     const int tj = blockIdx.x, t = tj / top;
@@ -178,8 +278,16 @@ moe_up_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w_up
     __syncthreads();
     const bool ok = e >= 0 && e < E;
     for (int f = blockIdx.y * rows_pb + warp; f < min(ff, (int)(blockIdx.y + 1) * rows_pb); f += MOE_WARPS) {
-        float z = ok ? dot_row<T>(w_up + ((size_t)e * ff + f) * hidden, xs, hidden, lane) : 0.f;
-        if (act == 0) { z = fmaxf(z, 0.f); z = z * z; } else { z = z / (1.f + expf(-z)); }
+        float z;
+        if (act == 2) {                             // a gated unit: ff gate rows, then ff up rows
+            const T* we = w_up + (size_t)e * 2 * ff * hidden;
+            const float g = ok ? dot_row<T>(we + (size_t)f * hidden, xs, hidden, lane) : 0.f;
+            const float u = ok ? dot_row<T>(we + (size_t)(ff + f) * hidden, xs, hidden, lane) : 0.f;
+            z = glu_unit(g, u, unit);
+        } else {
+            z = ok ? dot_row<T>(w_up + ((size_t)e * ff + f) * hidden, xs, hidden, lane) : 0.f;
+            if (act == 0) { z = fmaxf(z, 0.f); z = z * z; } else { z = z / (1.f + expf(-z)); }
+        }
         if (lane == 0) a[(size_t)tj * ff + f] = from_f32<T>(z);
     }
 }
@@ -205,9 +313,12 @@ moe_down_kernel(const T* __restrict__ a, const T* __restrict__ w_down, const int
 }
 
 extern "C" int gi_moe_up(const void* x, long long ldx, const void* w_up, const int* idx, void* a, int act_dtype, int n_rows,
-                         int top, int E, int ff, int hidden, int act, void* stream) {
+                         int top, int E, int ff, int hidden, int act, int unit_kind, float alpha, float gate_max,
+                         float up_limit, float up_shift, void* stream) {
+    const GluShape unit = {unit_kind, alpha, gate_max, up_limit, up_shift};
     GI_REQUIRE(n_rows >= 0 && top > 0 && E > 0 && ff > 0 && hidden > 0 && ldx >= hidden, "gi_moe_up: sizes");
-    GI_REQUIRE((ff + MOE_WARPS - 1) / MOE_WARPS <= 65535 && (act == 0 || act == 1), "gi_moe_up: %d rows per expert, activation %d", ff, act);
+    GI_REQUIRE((ff + MOE_WARPS - 1) / MOE_WARPS <= 65535 && act >= 0 && act <= 2, "gi_moe_up: %d rows per expert, activation %d", ff, act);
+    GI_REQUIRE(act != 2 || (unit_kind >= 0 && unit_kind <= 2 && up_limit >= 0.f), "gi_moe_up: gated unit %d", unit_kind);
     if (n_rows == 0) return 0;
     const size_t smem = (size_t)hidden * sizeof(float);
     const int rows_pb = moe_rows_per_block(n_rows * top, ff);
@@ -215,10 +326,10 @@ extern "C" int gi_moe_up(const void* x, long long ldx, const void* w_up, const i
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32) {
         if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)moe_up_kernel<float>, smem, "gi_moe_up"); if (rc) return rc; }
-        gi_launch(moe_up_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, s, (const float*)x, ldx, (const float*)w_up, idx, (float*)a, top, E, ff, hidden, act, rows_pb);
+        gi_launch(moe_up_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, s, (const float*)x, ldx, (const float*)w_up, idx, (float*)a, top, E, ff, hidden, act, rows_pb, unit);
     } else if (act_dtype == GI_DTYPE_BF16) {
         if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)moe_up_kernel<bf16>, smem, "gi_moe_up"); if (rc) return rc; }
-        gi_launch(moe_up_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, s, (const bf16*)x, ldx, (const bf16*)w_up, idx, (bf16*)a, top, E, ff, hidden, act, rows_pb);
+        gi_launch(moe_up_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, s, (const bf16*)x, ldx, (const bf16*)w_up, idx, (bf16*)a, top, E, ff, hidden, act, rows_pb, unit);
     } else {
         GI_REQUIRE(false, "gi_moe_up: activation dtype %d", act_dtype);
     }

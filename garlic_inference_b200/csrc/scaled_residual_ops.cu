@@ -5,8 +5,10 @@
 //                           no mean or variance is taken, alpha is one learned number; with write_residual the sum
 //                           goes back into x; `rows` picks input rows (nothing is written back then)
 //   gi_residual_add_scaled  x += delta * scale                                           (scale optional)
-//   gi_glu                  out = act(gate) * up for rows [gate | up];  act 0: silu, 1: gelu in its tanh form,
-//                           0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+//   gi_glu                  out = act(g) * (u + up_shift) for rows [gate | up] (out may be columns of a wider matrix), g = min(gate, gate_max),
+//                           u = clamp(up, -up_limit, up_limit) (infinite limits and a shift of 0: the plain unit);
+//                           act 0: silu, 1: gelu in its tanh form, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))),
+//                           2: z sigmoid(alpha z)
 //   gi_relu_squared         out = max(z, 0)^2
 //   gi_scaled_sum           out = a * ca + b * cb                                        (two mixers side by side)
 //
@@ -14,6 +16,7 @@
 // not depend on what else is in the launch.  NikolayBlagoev/garlic-inference has none of these (its layer is
 // pre-norm RMSNorm with a plain residual add, src/src-cuda/norm.cu:51-101).
 #include "common.cuh"
+#include "glu.cuh"
 #include <math.h>
 
 // ------------------------------------------------------------------ scaled add + Dynamic Tanh
@@ -88,26 +91,22 @@ extern "C" int gi_residual_add_scaled(const void* delta, int act_dtype, const vo
 }
 
 // ------------------------------------------------------------------ gated linear unit, squared relu
-__device__ __forceinline__ float glu_act(float z, int kind) {
-    if (kind == 0) return z / (1.f + expf(-z));
-    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-}
-
 template <typename T>
-__global__ void glu_kernel(const T* __restrict__ gate_up, long long ld, T* __restrict__ out, int n_rows, int inter, int kind) {
+__global__ void glu_kernel(const T* __restrict__ gate_up, long long ld, T* __restrict__ out, long long ld_out, int n_rows,
+                           int inter, GluShape p) {
     gi_pdl_start();
     const long long total = (long long)n_rows * inter;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const long long r = i / inter;
         const int c = (int)(i - r * inter);
         const T* row = gate_up + r * ld;
-        out[i] = from_f32<T>(glu_act(to_f32(row[c]), kind) * to_f32(row[inter + c]));
+        out[r * ld_out + c] = from_f32<T>(glu_unit(to_f32(row[c]), to_f32(row[inter + c]), p));
     }
 }
 
 // Eight columns at a time with 16-byte loads and stores (bfloat16 rows whose halves start on 16 bytes).
-__global__ void glu_vec_kernel(const bf16* __restrict__ gate_up, long long ld, bf16* __restrict__ out, int n_rows, int inter,
-                               int kind) {
+__global__ void glu_vec_kernel(const bf16* __restrict__ gate_up, long long ld, bf16* __restrict__ out, long long ld_out,
+                               int n_rows, int inter, GluShape p) {
     gi_pdl_start();
     const int per_row = inter / 8;
     const long long total = (long long)n_rows * per_row;
@@ -123,28 +122,30 @@ __global__ void glu_vec_kernel(const bf16* __restrict__ gate_up, long long ld, b
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const float2 gf = __bfloat1622float2(g2[k]), uf = __bfloat1622float2(u2[k]);
-            o2[k] = __floats2bfloat162_rn(glu_act(gf.x, kind) * uf.x, glu_act(gf.y, kind) * uf.y);
+            o2[k] = __floats2bfloat162_rn(glu_unit(gf.x, uf.x, p), glu_unit(gf.y, uf.y, p));
         }
-        *reinterpret_cast<uint4*>(out + r * inter + c) = o;
+        *reinterpret_cast<uint4*>(out + r * ld_out + c) = o;
     }
 }
 
-extern "C" int gi_glu(const void* gate_up, long long ld, void* out, int act_dtype, int n_rows, int inter, int kind,
-                      void* stream) {
-    GI_REQUIRE(n_rows >= 0 && inter > 0 && ld >= 2LL * inter && (kind == 0 || kind == 1), "gi_glu: sizes or activation");
+extern "C" int gi_glu(const void* gate_up, long long ld, void* out, long long ld_out, int act_dtype, int n_rows, int inter, int kind,
+                      float alpha, float gate_max, float up_limit, float up_shift, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && inter > 0 && ld >= 2LL * inter && ld_out >= inter && kind >= 0 && kind <= 2, "gi_glu: sizes or activation");
+    GI_REQUIRE(up_limit >= 0.f, "gi_glu: the up half is clamped to +-%f", (double)up_limit);
     if (n_rows == 0) return 0;
+    const GluShape p = {kind, alpha, gate_max, up_limit, up_shift};
     const long long total = (long long)n_rows * inter;
     const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32)
-        gi_launch(glu_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gate_up, ld, (float*)out, n_rows, inter, kind);
-    else if (act_dtype == GI_DTYPE_BF16 && inter % 8 == 0 && ld % 8 == 0 && (uintptr_t)gate_up % 16 == 0 &&
+        gi_launch(glu_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gate_up, ld, (float*)out, ld_out, n_rows, inter, p);
+    else if (act_dtype == GI_DTYPE_BF16 && inter % 8 == 0 && ld % 8 == 0 && ld_out % 8 == 0 && (uintptr_t)gate_up % 16 == 0 &&
              (uintptr_t)out % 16 == 0) {
         const long long units = total / 8;
         const int vb = (int)((units + 255) / 256 > 148 * 16 ? 148 * 16 : (units + 255) / 256);
-        gi_launch(glu_vec_kernel, dim3(vb), dim3(256), 0, s, (const bf16*)gate_up, ld, (bf16*)out, n_rows, inter, kind);
+        gi_launch(glu_vec_kernel, dim3(vb), dim3(256), 0, s, (const bf16*)gate_up, ld, (bf16*)out, ld_out, n_rows, inter, p);
     } else if (act_dtype == GI_DTYPE_BF16)
-        gi_launch(glu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)gate_up, ld, (bf16*)out, n_rows, inter, kind);
+        gi_launch(glu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)gate_up, ld, (bf16*)out, ld_out, n_rows, inter, p);
     else
         GI_REQUIRE(false, "gi_glu: activation dtype %d", act_dtype);
     return gi_check_launch("gi_glu");

@@ -147,6 +147,7 @@ class DecoderModel:
         `want_rows` (int32 row indices), or None when nothing is wanted."""
         ctx.residual_act = None                      # a context may be run again (recording a decode step)
         ctx.delta_scale = None
+        ctx.delta_extra = None
         residual = self.embedding.step(ctx)
         for pos in self.positions.values():
             pos.on_embedding(residual, ctx)
@@ -157,6 +158,8 @@ class DecoderModel:
         if want_rows is None or want_rows.numel() == 0:
             return None
         scaled = {"delta_scale": ctx.delta_scale} if ctx.delta_scale is not None and delta is not None else {}
+        if ctx.delta_extra is not None:
+            scaled["delta2"] = ctx.delta_extra
         normed = self.final_norm.add_norm(delta, residual, rows=want_rows, **scaled)
         return self.head.step(normed)
 

@@ -90,6 +90,53 @@ def add_rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: t
     return out
 
 
+def add_layernorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor,
+                  bias: Optional[torch.Tensor], eps: float, act_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+                  write_residual: bool = True, delta2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """(s - mean(s)) / sqrt(var(s) + eps) * weight (+ bias) for s = residual (+ delta (+ delta2)), in `act_dtype`; the
+    float32 sum goes back into `residual` unless `rows` (int32) picks rows or `write_residual` is False."""
+    l = require_gpu()
+    _dense(residual, "residual", torch.float32), _dense(weight, "weight")
+    dim = residual.shape[-1]
+    if weight.numel() != dim or (bias is not None and _dense(bias, "bias", weight.dtype).numel() != dim):
+        raise KernelError(f"norm weight of {weight.numel()} elements for rows of {dim}")
+    for d, name in ((delta, "delta"), (delta2, "delta2")):
+        if d is not None and _dense(d, name, act_dtype).shape != residual.shape:
+            raise KernelError(f"{name} {tuple(d.shape)} and residual {tuple(residual.shape)} differ")
+    if rows is not None:
+        _dense(rows, "rows", torch.int32)
+        n_rows, write_residual = rows.numel(), False
+    else:
+        n_rows = residual.numel() // dim
+    out = torch.empty((n_rows, dim), dtype=act_dtype, device=residual.device)
+    check(l.gi_add_layernorm(_ptr(delta), _ptr(delta2), _ptr(residual), _ptr(weight), _ptr(bias), code(weight.dtype),
+                             _ptr(out), code(act_dtype), _ptr(rows), n_rows, dim, float(eps), int(write_residual),
+                             _stream()), l)
+    return out
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """x / sqrt(mean(x^2) + eps) * weight for the rows of x, which may be columns of a wider matrix; dense result in
+    x's type, float32 inside."""
+    l = require_gpu()
+    _rows(x, "x"), _dense(weight, "weight")
+    n, dim = x.shape
+    if weight.numel() != dim:
+        raise KernelError(f"norm weight of {weight.numel()} elements for rows of {dim}")
+    out = torch.empty((n, dim), dtype=x.dtype, device=x.device)
+    check(l.gi_rmsnorm_rows(_ptr(x), x.stride(0), _ptr(weight), code(weight.dtype), _ptr(out), code(x.dtype), n, dim,
+                            float(eps), _stream()), l)
+    return out
+
+
+def softcap_(z: torch.Tensor, cap: float) -> torch.Tensor:
+    """z <- cap * tanh(z / cap) in place (float32)."""
+    l = require_gpu()
+    _dense(z, "z", torch.float32)
+    check(l.gi_softcap(_ptr(z), z.numel(), float(cap), _stream()), l)
+    return z
+
+
 def residual_add(delta: torch.Tensor, residual: torch.Tensor) -> None:
     l = require_gpu()
     _dense(delta, "delta")
@@ -330,14 +377,34 @@ def residual_add_scaled(delta: torch.Tensor, delta_scale: Optional[torch.Tensor]
                                    _stream()), l)
 
 
-def glu(gate_up: torch.Tensor, activation: str) -> torch.Tensor:
-    """act(gate) * up for rows [gate | up]; activation "silu" or "gelu_tanh"."""
+GLU_KINDS = {"silu": 0, "gelu_tanh": 1, "swish": 2}
+
+
+def glu_shape(activation: str, swish_alpha: float = 1.0, gate_max: Optional[float] = None,
+              up_limit: Optional[float] = None, up_shift: float = 0.0) -> tuple:
+    """The gated unit act(min(gate, gate_max)) * (clamp(up, -up_limit, up_limit) + up_shift) as the kernels take it:
+    (kind, alpha, gate_max, up_limit, up_shift); a limit of None is none."""
+    if activation not in GLU_KINDS:
+        raise KernelError(f"gated-unit activation {activation!r} is none of {sorted(GLU_KINDS)}")
+    inf = float("inf")
+    return (GLU_KINDS[activation], float(swish_alpha), inf if gate_max is None else float(gate_max),
+            inf if up_limit is None else float(up_limit), float(up_shift))
+
+
+def glu(gate_up: torch.Tensor, activation, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """unit(gate, up) for rows [gate | up]; `activation` is "silu", "gelu_tanh" or "swish" (plain act(gate) * up), or a
+    `glu_shape` tuple with limits and a shift.  `out` may be columns of a wider matrix."""
     l = require_gpu()
     _rows(gate_up, "gate_up")
     n, two_i = gate_up.shape
-    out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
-    check(l.gi_glu(_ptr(gate_up), gate_up.stride(0), _ptr(out), code(gate_up.dtype), n, two_i // 2,
-                   {"silu": 0, "gelu_tanh": 1}[activation], _stream()), l)
+    shape = glu_shape(activation) if isinstance(activation, str) else activation
+    if out is None:
+        out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _rows(out, "out", gate_up.dtype)
+    if out.shape != (n, two_i // 2):
+        raise KernelError(f"out {tuple(out.shape)} for a result of {(n, two_i // 2)}")
+    check(l.gi_glu(_ptr(gate_up), gate_up.stride(0), _ptr(out), out.stride(0), code(gate_up.dtype), n, two_i // 2, *shape,
+                   _stream()), l)
     return out
 
 
@@ -383,21 +450,40 @@ def router_topk(logits: torch.Tensor, top: int):
     return idx, wt
 
 
+def router_select(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float):
+    """Scores = softmax of the float32 `logits` over all experts; of `groups` equal groups of neighbouring experts the
+    `keep` with the largest best score stay; (the `top` experts with the largest scores among those int32 [n, top] in
+    falling order, their scores times `scale` float32): no renormalisation."""
+    l = require_gpu()
+    _rows(logits, "logits", torch.float32)
+    n, E = logits.shape
+    idx = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    wt = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    check(l.gi_router_select(_ptr(logits), logits.stride(0), E, int(top), int(groups), int(keep), float(scale), _ptr(idx),
+                             _ptr(wt), n, _stream()), l)
+    return idx, wt
+
+
 def moe_rowwise(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor,
-                activation: str) -> torch.Tensor:
+                activation) -> torch.Tensor:
     """sum_j wt[t, j] W_down[idx[t, j]] act(W_up[idx[t, j]] x[t]) with the chosen experts read from device memory:
-    w_up [E, ff, hidden], w_down [E, hidden, ff]; one row of x at a time (decode steps)."""
+    w_up [E, ff, hidden] and `activation` "relu_squared" or "silu", or w_up [E, 2 ff, hidden] (gate rows, then up
+    rows) and a `glu_shape` tuple; w_down [E, hidden, ff]; one row of x at a time (decode steps)."""
     l = require_gpu()
     _rows(x, "x"), _dense(w_up, "w_up", x.dtype), _dense(w_down, "w_down", x.dtype)
     _dense(idx, "idx", torch.int32), _dense(wt, "wt", torch.float32)
     n, hidden = x.shape
-    E, ff, _ = w_up.shape
+    E, _, ff = w_down.shape
     top = idx.shape[1]
+    gated = not isinstance(activation, str)
+    if w_up.shape != (E, (2 if gated else 1) * ff, hidden):
+        raise KernelError(f"expert matrices {tuple(w_up.shape)} and {tuple(w_down.shape)} do not fit each other")
     a = torch.empty((n, top, ff), dtype=x.dtype, device=x.device)
     part = torch.empty((n * top, hidden), dtype=x.dtype, device=x.device)
-    act = {"relu_squared": 0, "silu": 1}[activation]
+    act = 2 if gated else {"relu_squared": 0, "silu": 1}[activation]
+    unit = activation if gated else glu_shape("silu")
     check(l.gi_moe_up(_ptr(x), x.stride(0), _ptr(w_up), _ptr(idx), _ptr(a), code(x.dtype), n, top, E, ff, hidden, act,
-                      _stream()), l)
+                      *unit, _stream()), l)
     check(l.gi_moe_down(_ptr(a), _ptr(w_down), _ptr(idx), _ptr(part), code(x.dtype), n, top, E, ff, hidden, _stream()), l)
     return moe_combine(part, None, wt)
 
@@ -637,29 +723,38 @@ def latent_decode(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor
     return out
 
 
-def latent_prepare(proj: torch.Tensor, q_off: int, c_off: int, q_lat: torch.Tensor, norm_w: torch.Tensor, eps: float,
-                   freq: torch.Tensor, magnitude: float, n_rot: int, tok_pos: torch.Tensor, tok_slot: torch.Tensor,
-                   block_table: torch.Tensor, pool: torch.Tensor, n_heads: int, plain_dim: int, rot_dim: int,
-                   rank: int, status: torch.Tensor, append: bool = True) -> torch.Tensor:
+def latent_prepare(q_src: torch.Tensor, q_off: int, kv_src: Optional[torch.Tensor], c_off: int, q_lat: torch.Tensor,
+                   norm_w: Optional[torch.Tensor], eps: float, freq: torch.Tensor, magnitude: float, n_rot: int,
+                   tok_pos: torch.Tensor, tok_slot: torch.Tensor, block_table: torch.Tensor, pool: torch.Tensor,
+                   n_heads: int, plain_dim: int, rot_dim: int, rank: int, status: torch.Tensor, append: bool = True,
+                   half_layout: bool = False) -> torch.Tensor:
     """Latent attention between projections and attention: writes each token's cache row [normed latent | rotated
-    shared key part | zeros] into `pool` [pages, 1, page_size, row] and returns the queries [n, heads, row] =
-    [q' | rotated part | zeros], q' = `q_lat` [n, heads, rank]."""
+    shared key part | zeros] into `pool` [pages, 1, page_size, row] from columns c_off .. of `kv_src` (None for a
+    layer that reads rows another layer cached) and returns the queries [n, heads, row] = [q' | rotated part |
+    zeros], q' = `q_lat` [n, heads, rank], the rotated part from `q_src`'s columns (heads of plain_dim + rot_dim from
+    q_off on).  `half_layout`: dimension i turns with i + n_rot/2 instead of 2i with 2i + 1."""
     l = require_gpu()
-    act = proj.dtype
-    _rows(proj, "proj"), _dense(q_lat, "q_lat", act), _dense(norm_w, "norm_w"), _dense(freq, "freq", torch.float32)
+    act = q_src.dtype
+    _rows(q_src, "q_src"), _dense(q_lat, "q_lat", act), _dense(freq, "freq", torch.float32)
     _dense(pool, "pool", act)
+    if kv_src is not None:
+        _rows(kv_src, "kv_src", act), _dense(norm_w, "norm_w")
+    elif append:
+        raise KernelError("latent_prepare: nothing to append without a latent")
     for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (block_table, "block_table"), (status, "status")):
         _dense(t, name, torch.int32)
-    n = proj.shape[0]
+    n = q_src.shape[0]
     n_pages, one, page_size, row_w = pool.shape
-    if one != 1 or q_lat.shape != (n, n_heads, rank) or norm_w.numel() != rank or freq.numel() * 2 != n_rot:
+    if one != 1 or q_lat.shape != (n, n_heads, rank) or freq.numel() * 2 != n_rot or \
+            (kv_src is not None and norm_w.numel() != rank):
         raise KernelError("latent_prepare: the pool, q_lat, the norm weight or the frequencies do not fit the sizes")
-    q_out = torch.empty((n, n_heads, row_w), dtype=act, device=proj.device)
-    check(l.gi_latent_prepare(_ptr(proj), proj.stride(0), q_off, c_off, _ptr(q_lat), code(act), _ptr(norm_w),
-                              code(norm_w.dtype), float(eps), _ptr(freq), float(magnitude), n_rot, _ptr(tok_pos),
-                              _ptr(tok_slot), _ptr(block_table), _ptr(pool), _ptr(q_out), n, n_heads, plain_dim,
-                              rot_dim, rank, row_w, page_size, block_table.shape[1], n_pages, int(append),
-                              _ptr(status), _stream()), l)
+    q_out = torch.empty((n, n_heads, row_w), dtype=act, device=q_src.device)
+    check(l.gi_latent_prepare(_ptr(q_src), q_src.stride(0), q_off, _ptr(kv_src), kv_src.stride(0) if kv_src is not None else 0,
+                              c_off, int(half_layout), _ptr(q_lat), code(act), _ptr(norm_w),
+                              code(norm_w.dtype) if norm_w is not None else F32, float(eps), _ptr(freq), float(magnitude),
+                              n_rot, _ptr(tok_pos), _ptr(tok_slot), _ptr(block_table), _ptr(pool), _ptr(q_out), n, n_heads,
+                              plain_dim, rot_dim, rank, row_w, page_size, block_table.shape[1], n_pages,
+                              int(append and kv_src is not None), _ptr(status), _stream()), l)
     return q_out
 
 

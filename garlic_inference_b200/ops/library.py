@@ -37,12 +37,16 @@ _SIGNATURES = {
     "gi_attn_finish": ([P, I, I, P, F, I, F, P, L, P, L, I, I, I, I, P], I),
     "gi_add_dyt": ([P, P, I, P, P, P, P, I, P, I, P, I, I, I, P], I),
     "gi_residual_add_scaled": ([P, I, P, I, P, I, I, P], I),
-    "gi_glu": ([P, L, P, I, I, I, I, P], I),
+    "gi_glu": ([P, L, P, L, I, I, I, I, F, F, F, F, P], I),
+    "gi_add_layernorm": ([P, P, P, P, P, I, P, I, P, I, I, F, I, P], I),
+    "gi_rmsnorm_rows": ([P, L, P, I, P, I, I, I, F, P], I),
+    "gi_softcap": ([P, L, F, P], I),
+    "gi_router_select": ([P, L, I, I, I, I, F, P, P, I, P], I),
     "gi_relu_squared": ([P, P, I, L, P], I),
     "gi_scaled_sum": ([P, F, P, F, P, I, L, P], I),
     "gi_router_logits": ([P, L, I, P, P, I, I, I, P], I),
     "gi_router_topk": ([P, L, I, I, P, P, I, P], I),
-    "gi_moe_up": ([P, L, P, P, P, I, I, I, I, I, I, I, P], I),
+    "gi_moe_up": ([P, L, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, P], I),
     "gi_moe_down": ([P, P, P, P, I, I, I, I, I, I, P], I),
     "gi_moe_group": ([P, P, L, I, P, P, P, P, I, I, I, I, P], I),
     "gi_moe_combine": ([P, P, P, P, I, I, I, I, P], I),
@@ -56,7 +60,7 @@ _SIGNATURES = {
     "gi_delta_scan": ([P, L, I, I, I, P, L, I, I, P, L, P, P, I, P, L, P, P, P, I, I, I, I, I, F, F, I, P], I),
     "gi_causal_sink_softmax": ([P, L, P, L, I, I, I, I, I, F, P, I, P], I),
     "gi_latent_decode": ([P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P], I),
-    "gi_latent_prepare": ([P, L, I, I, P, I, P, I, F, P, F, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P], I),
+    "gi_latent_prepare": ([P, L, I, P, L, I, I, P, I, P, I, F, P, F, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P], I),
     "gi_attention_prefill_bf16": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, P], I),
     "gi_attention_prefill_masked_bf16": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, I, F, P], I),
     "gi_attention_decode_masked_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P], I),

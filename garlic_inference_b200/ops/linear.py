@@ -114,11 +114,12 @@ def swiglu_product(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     return kernels.swiglu(linear(x, w_gate_up))
 
 
-def per_head_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+def per_head_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y[n, h, :] = w[h] x[n, h, :] for a weight [heads, out, in] and x [n, heads, in], whose heads and rows may lie
     apart (columns of a wider product's output) while each head's `in` values are dense; returns dense
     [n, heads, out].  float32: this package's float32 kernel, head by head, reading and writing in place;
-    bfloat16: the library's batched product (float32 accumulation)."""
+    bfloat16: the library's batched product (float32 accumulation), the result left in float32 when `out_dtype`
+    says so."""
     if x.dim() != 3 or w.dim() != 3 or x.shape[1] != w.shape[0] or x.shape[2] != w.shape[2] or x.stride(2) != 1:
         raise KernelError(f"per_head_linear: x {tuple(x.shape)} (strides {x.stride()}) does not fit a weight {tuple(w.shape)}")
     n, heads, k = x.shape
@@ -133,4 +134,6 @@ def per_head_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     if w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
         raise KernelError(f"per_head_linear: weight {w.dtype}, activations {x.dtype}")
     kernels.require_gpu()
+    if out_dtype == torch.float32:
+        return torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32).transpose(0, 1).contiguous()
     return torch.bmm(x.transpose(0, 1), w.transpose(1, 2)).transpose(0, 1).contiguous()

@@ -2,7 +2,7 @@
 from .base import (Block, Embedding, FeedForward, Gate, Head, Mixer, Norm, Part, PositionEncoding, Runtime,
                    StepContext, StepShape, known_parts, part_class, register_part)
 from .attention import GQAAttention
-from .block import (ChannelScale, LinearHead, PostNormGatedResidualBlock, PreNormResidualBlock,
+from .block import (ChannelScale, LinearHead, ParallelResidualBlock, PostNormGatedResidualBlock, PreNormResidualBlock,
                     PreNormScaledResidualBlock, SigmoidGate, TokenEmbedding)
 from .delta_rule import GatedDeltaRule
 from .latent_attention import LatentAttention
@@ -10,7 +10,7 @@ from .linear_attention import DecayLinearAttention
 from .masked_attention import MaskedAttention
 from .mlp import GluMLP, SwiGLUMLP, XieluMLP
 from .moe import RoutedExperts
-from .norm import DynamicTanhNorm, RMSNorm
+from .norm import DynamicTanhNorm, LayerNorm, RMSNorm
 from .parallel import ParallelMixers
 from .rotary import RotaryPositions
 
@@ -19,4 +19,4 @@ __all__ = ["Block", "Embedding", "FeedForward", "Gate", "Head", "PostNormGatedRe
            "Runtime", "StepContext", "StepShape", "known_parts", "part_class", "register_part", "GQAAttention",
            "LinearHead", "PreNormResidualBlock", "TokenEmbedding", "SwiGLUMLP", "RMSNorm", "RotaryPositions",
            "ChannelScale", "PreNormScaledResidualBlock", "MaskedAttention", "GluMLP", "RoutedExperts",
-           "DynamicTanhNorm", "ParallelMixers"]
+           "DynamicTanhNorm", "ParallelMixers", "ParallelResidualBlock", "LayerNorm"]

@@ -109,6 +109,9 @@ class StepContext:
     # A factor per channel (float32 or the weights' type, [hidden]) that the pending delta is multiplied by when
     # it is added to the stream, set by blocks whose sublayer results join through a learned scale; None: 1.
     delta_scale: Optional[torch.Tensor] = None
+    # A second pending result in the activation type that joins the stream together with the pending delta (blocks
+    # whose mixer and feed-forward read one normed input); the next norm adds both in float32.  None: nothing.
+    delta_extra: Optional[torch.Tensor] = None
 
     def seq_spans(self) -> Optional[torch.Tensor]:
         """int32 [n_seq, 3] = {slot, first row, rows} on the device for kernels that walk each sequence's rows
@@ -172,9 +175,10 @@ class FeedForward(Part):
 
 
 class Norm(Part):
-    def add_norm(self, delta, residual, rows=None, write_residual=True, delta_scale=None):
-        """normed(residual + delta * delta_scale); `delta_scale` (a factor per channel) is only passed by
-        arrangements that scale their sublayers' results, so a norm for other arrangements may leave it out."""
+    def add_norm(self, delta, residual, rows=None, write_residual=True, delta_scale=None, delta2=None):
+        """normed(residual + delta * delta_scale + delta2); `delta_scale` (a factor per channel) is only passed by
+        arrangements that scale their sublayers' results and `delta2` (a second pending result) only by arrangements
+        that leave two, so a norm for other arrangements may leave them out."""
         raise NotImplementedError
 
 

@@ -18,6 +18,14 @@ scale) on each sublayer's result:
     h += s1 * mixer(norm_in(h));  h += s2 * ffn(norm_post(h))
 The scaled add happens inside the norm that follows, in float32; the block returns its last result pending and
 leaves the factor it still has to be multiplied by in `ctx.delta_scale`.  The feed-forward may be absent.
+
+`parallel_residual` (no upstream counterpart): one norm, read by the mixer and the feed-forward alike, whose
+results join the stream together:
+    x = norm_in(h);  h += mixer(x) + ffn(x)
+Both results stay pending (`ctx.delta_extra` carries the second) and the next norm adds them in float32.  When
+both sublayers end in an output projection and can hand over what goes into it (`pre_output` with `w_o` /
+`w_down`), the two projections and the sum are one product over activations and weights laid side by side, summed
+in float32 inside the product.  The feed-forward may be absent.
 """
 from __future__ import annotations
 
@@ -35,7 +43,15 @@ def settle_scaled(delta, residual, ctx):
         kernels.residual_add_scaled(delta, ctx.delta_scale, residual)
         delta = None
     ctx.delta_scale = None
+    settle_extra(residual, ctx)
     return delta
+
+
+def settle_extra(residual, ctx):
+    """A second pending result (left by a block whose sublayers run side by side) is added to the stream now."""
+    if ctx.delta_extra is not None:
+        kernels.residual_add(ctx.delta_extra, residual)
+        ctx.delta_extra = None
 
 
 class PreNormResidualBlock(Block):
@@ -187,6 +203,7 @@ class PreNormScaledResidualBlock(Block):
 
     def step(self, delta, residual, ctx, cache, writes_cache=True):
         ctx.residual_act = None
+        settle_extra(residual, ctx)
         scale = lambda g: g.weight if g is not None else None
         x = self.norm_in.add_norm(delta, residual, delta_scale=ctx.delta_scale if delta is not None else None)
         y = self.mixer.step(x, ctx, cache, self.position, writes_cache)
@@ -196,6 +213,56 @@ class PreNormScaledResidualBlock(Block):
             y = self.feed_forward.step(x, ctx)
             ctx.delta_scale = scale(self.scale_ff)
         return y
+
+
+class ParallelResidualBlock(Block):
+    kind = "parallel_residual"
+
+    def __init__(self, mixer, feed_forward, norms, position, rt):
+        self.rt = rt
+        self.mixer, self.feed_forward, self.position = mixer, feed_forward, position
+        if "input" not in norms:
+            raise ValueError("block 'parallel_residual' needs the norm 'input'")
+        self.norm_in = norms["input"]
+        # one output product for both sublayers when each can hand over what goes into its own
+        self.w_out = None
+        ff = feed_forward
+        if ff is not None and hasattr(mixer, "pre_output") and getattr(mixer, "w_o", None) is not None and \
+                hasattr(ff, "pre_output") and getattr(ff, "w_down", None) is not None and \
+                mixer.w_o.dtype == ff.w_down.dtype and mixer.w_o.shape[1] % 8 == 0:
+            self.k_mixer = mixer.w_o.shape[1]
+            self.w_out = torch.cat([mixer.w_o, ff.w_down], dim=1).contiguous()
+            mixer.w_o = ff.w_down = None             # the sublayers' own copies are let go: only pre_output runs
+
+    def cache_requirement(self):
+        return self.mixer.cache_requirement()
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in (self.mixer, self.feed_forward, self.norm_in, self.position) if p is not None)
+
+    def step_arrays(self, shape, cache):
+        ff = self.feed_forward.step_arrays(shape, cache) if self.feed_forward is not None else {}
+        return {**self.mixer.step_arrays(shape, cache), **ff}
+
+    def step(self, delta, residual, ctx, cache, writes_cache=True):
+        ctx.residual_act = None
+        if delta is not None and ctx.delta_scale is not None:
+            kernels.residual_add_scaled(delta, ctx.delta_scale, residual)
+            delta = None
+        ctx.delta_scale = None
+        extra, ctx.delta_extra = ctx.delta_extra, None
+        x = self.norm_in.add_norm(delta, residual, **({"delta2": extra} if extra is not None else {}))
+        if self.w_out is not None:
+            acts = torch.empty((x.shape[0], self.w_out.shape[1]), dtype=self.rt.dtype, device=x.device)
+            self.mixer.pre_output(x, ctx, cache, self.position, writes_cache, out=acts[:, :self.k_mixer])
+            self.feed_forward.pre_output(x, ctx, out=acts[:, self.k_mixer:])
+            return linear(acts, self.w_out)
+        y = self.mixer.step(x, ctx, cache, self.position, writes_cache)
+        if self.feed_forward is None:
+            return y
+        ctx.delta_extra = y
+        return self.feed_forward.step(x, ctx)
 
 
 class TokenEmbedding(Embedding):
@@ -218,7 +285,8 @@ class TokenEmbedding(Embedding):
 
 
 class LinearHead(Head):
-    """logits = normed . W^T as float32 (src/models/qwen3/qwen3.cpp:302-303), on the rows asked for only."""
+    """logits = normed . W^T as float32 (src/models/qwen3/qwen3.cpp:302-303), on the rows asked for only.  With
+    `softcap` c the logits become c * tanh(logits / c) (upstream has no cap)."""
     kind = "linear_head"
     graph_safe = True
 
@@ -229,14 +297,17 @@ class LinearHead(Head):
     def __init__(self, params, load, rt):
         super().__init__(params, load, rt)
         self.weight = load("weight")
+        self.softcap = float(params["softcap"]) if params.get("softcap") else None
 
     def step(self, normed):
-        return linear(normed, self.weight, out_dtype=torch.float32)
+        logits = linear(normed, self.weight, out_dtype=torch.float32)
+        return kernels.softcap_(logits, self.softcap) if self.softcap else logits
 
 
 register_part(PreNormResidualBlock.kind, PreNormResidualBlock)
 register_part(PostNormGatedResidualBlock.kind, PostNormGatedResidualBlock)
 register_part(PreNormScaledResidualBlock.kind, PreNormScaledResidualBlock)
+register_part(ParallelResidualBlock.kind, ParallelResidualBlock)
 register_part(SigmoidGate.kind, SigmoidGate)
 register_part(ChannelScale.kind, ChannelScale)
 register_part(TokenEmbedding.kind, TokenEmbedding)

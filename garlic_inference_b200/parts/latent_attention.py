@@ -1,11 +1,16 @@
 """Attention whose keys and values are expanded from a cached low-rank latent, as a mixer.
 
     q = Wq x = per head [ plain_dim unrotated | rot_dim rotated ]
+        with `q_rank`:  q = Wuq ( rmsnorm(Wdq x) * w ), the queries through a normed latent of their own
     [c | kr] = Wdkv x;  c <- rmsnorm(c) * w  (kv_rank);  kr (rot_dim): one rotated key part shared by all heads
     head h:  key = [ Wuk,h c | rot(kr) ],  value = Wuv,h c
     score = (q_plain . Wuk,h c + rot(q_rot) . rot(kr)) * softmax_scale,  causal
     softmax whose denominator also holds exp(sink_h) (optional, one learned number per head)
-    y = Wo concat_h( sum_j p_j Wuv,h c_j )
+    o_h = sum_j p_j Wuv,h c_j;  with `head_gate`:  o_h <- o_h * sigmoid(Wg x)_h, one number per head from the mixer's input
+    y = Wo concat_h( o_h )
+
+With `own_kv` False the layer has no Wdkv: the schedule points it at another layer's cache entry, whose rows (the
+normed latent and the rotated key part as that layer cached them) it reads with its own Wuk, Wuv and queries.
 
 Only c and rot(kr) are cached: one row per position in a single-plane paged entry.  The expansion is never
 materialised: q'_h = Wuk,h^T q_plain,h is made by a per-head product, attention runs over the cached rows for
@@ -22,8 +27,8 @@ float32) is this package's kernel, and the weighted sum is a second product [tok
 kv_rank]; the sequence's rows are gathered from its pages once per step and the tokens are cut into blocks
 whose scores fit `SCORE_BYTES`.  Tensor cores do both products; the weights are rounded to bfloat16 only as
 the second product's operand.
-The rotation is the position part's (its frequencies, magnitude and layout; this mixer's kernel pairs
-dimension 2i with 2i+1).  Upstream has grouped-query attention only (src/models/qwen3/qwen3.cpp:140-179).
+The rotation is the position part's (its frequencies, magnitude and layout: pairs (2i, 2i+1), or halves (i,
+i + n/2)).  Upstream has grouped-query attention only (src/models/qwen3/qwen3.cpp:140-179).
 """
 from __future__ import annotations
 
@@ -49,8 +54,16 @@ class LatentAttention(Mixer):
     def wanted(cls, params):
         hid, H, d, dr, dv, r = (params[k] for k in ("hidden_size", "n_heads", "plain_dim", "rot_dim", "value_dim",
                                                     "kv_rank"))
-        w = {"q": TensorWant((H * (d + dr), hid)), "dkv": TensorWant((r + dr, hid)), "dkv.norm": TensorWant((r,), "norm"),
-             "uk": TensorWant((H * d, r)), "uv": TensorWant((H * dv, r)), "o": TensorWant((hid, H * dv))}
+        w = {"uk": TensorWant((H * d, r)), "uv": TensorWant((H * dv, r)), "o": TensorWant((hid, H * dv))}
+        if params.get("q_rank"):
+            qr = params["q_rank"]
+            w.update({"dq": TensorWant((qr, hid)), "dq.norm": TensorWant((qr,), "norm"), "uq": TensorWant((H * (d + dr), qr))})
+        else:
+            w["q"] = TensorWant((H * (d + dr), hid))
+        if params.get("own_kv", True):
+            w.update({"dkv": TensorWant((r + dr, hid)), "dkv.norm": TensorWant((r,), "norm")})
+        if params.get("head_gate", False):
+            w["g"] = TensorWant((H, hid))
         if params.get("sink", False):
             w["sink"] = TensorWant((H,), std_scale=20.0)
         return w
@@ -60,10 +73,19 @@ class LatentAttention(Mixer):
         self.hidden, self.H = int(params["hidden_size"]), int(params["n_heads"])
         self.d, self.dr, self.dv, self.rank = (int(params[k]) for k in ("plain_dim", "rot_dim", "value_dim", "kv_rank"))
         self.scale, self.eps = float(params["softmax_scale"]), float(params["eps"])
+        self.q_rank = int(params.get("q_rank") or 0)
+        self.own_kv, self.head_gate = bool(params.get("own_kv", True)), bool(params.get("head_gate", False))
         self.row = -(-(self.rank + self.dr) // 8) * 8             # a cache row, padded for the kernel's 16-byte loads
-        self.w_in, (self.q_off, self.c_off) = pack_rows(
-            load, (("q", self.H * (self.d + self.dr)), ("dkv", self.rank + self.dr)), self.hidden, rt)
-        self.c_norm = load("dkv.norm")
+        # everything that reads the mixer's input is one product: [queries or their latent | latent and key part | gates]
+        packed = [("dq", self.q_rank) if self.q_rank else ("q", self.H * (self.d + self.dr))]
+        packed += [("dkv", self.rank + self.dr)] if self.own_kv else []
+        packed += [("g", self.H)] if self.head_gate else []
+        self.w_in, offs = pack_rows(load, packed, self.hidden, rt)
+        self.q_off = offs[0]
+        self.c_off = offs[1] if self.own_kv else None
+        self.g_off = offs[-1] if self.head_gate else None
+        self.q_norm, self.w_uq = (load("dq.norm"), load("uq")) if self.q_rank else (None, None)
+        self.c_norm = load("dkv.norm") if self.own_kv else None
         # Wuk per head as [rank, plain_dim]: the product q'_h = Wuk,h^T q_h in the [out, in] form of the others
         self.w_uk_t = load("uk").view(self.H, self.d, self.rank).transpose(1, 2).contiguous()
         self.w_uv = load("uv").view(self.H, self.dv, self.rank)
@@ -77,29 +99,47 @@ class LatentAttention(Mixer):
     def _rotation(self, position, device):
         if position is not None:
             freq, magnitude, n_rot, layout = position.rotary_frequencies()
-            if layout != "interleaved":
-                raise ValueError("latent_attention rotates pairs (2i, 2i+1): the position part must be 'interleaved'")
             if n_rot > self.dr:
                 raise ValueError(f"{n_rot} rotated dimensions of a key part of {self.dr}")
-            return freq, magnitude, n_rot
+            return freq, magnitude, n_rot, layout == "half"
         if self._no_rotation is None:
             self._no_rotation = torch.zeros(0, dtype=torch.float32, device=device)
-        return self._no_rotation, 1.0, 0
+        return self._no_rotation, 1.0, 0, False
 
     def step(self, x, ctx, cache, position, writes_cache=True):
-        kv = cache.kv
-        n = x.shape[0]
-        freq, magnitude, n_rot = self._rotation(position, x.device)
-        proj = linear(x, self.w_in)
-        q = proj[:, self.q_off:self.q_off + self.H * (self.d + self.dr)].view(n, self.H, self.d + self.dr)
-        q_lat = per_head_linear(q[:, :, :self.d], self.w_uk_t)                       # [n, H, rank]
-        q_rows = kernels.latent_prepare(proj, self.q_off, self.c_off, q_lat, self.c_norm, self.eps, freq, magnitude,
-                                        n_rot, ctx.tok_pos, ctx.tok_slot, kv.block_table, kv.k_pool, self.H, self.d,
-                                        self.dr, self.rank, ctx.status, append=writes_cache)
-        o_lat = self.attend(q_rows, kv, ctx)
-        o = per_head_linear(o_lat.view(n, self.H, self.rank), self.w_uv)             # [n, H, value_dim]
-        return linear(o.view(n, self.H * self.dv), self.w_o)
+        return linear(self.pre_output(x, ctx, cache, position, writes_cache), self.w_o)
 
+    def pre_output(self, x, ctx, cache, position, writes_cache=True, out=None, out_mul=1.0):
+        """Everything before the output projection: [n, n_heads * value_dim] in the activation type, times
+        `out_mul`, written into `out` (columns of a wider matrix) when given."""
+        kv = cache.kv
+        if self.own_kv != bool(writes_cache):
+            raise ValueError("a layer with a latent of its own writes its cache entry, and one without reads another "
+                             "layer's: the schedule says otherwise")
+        n = x.shape[0]
+        freq, magnitude, n_rot, half = self._rotation(position, x.device)
+        proj = linear(x, self.w_in)
+        if self.q_rank:
+            q_src, q_off = linear(kernels.rmsnorm_rows(proj[:, self.q_off:self.q_off + self.q_rank], self.q_norm, self.eps),
+                                  self.w_uq), 0
+        else:
+            q_src, q_off = proj, self.q_off
+        q = q_src[:, q_off:q_off + self.H * (self.d + self.dr)].view(n, self.H, self.d + self.dr)
+        q_lat = per_head_linear(q[:, :, :self.d], self.w_uk_t)                       # [n, H, rank]
+        q_rows = kernels.latent_prepare(q_src, q_off, proj if self.own_kv else None, self.c_off or 0, q_lat, self.c_norm,
+                                        self.eps, freq, magnitude, n_rot, ctx.tok_pos, ctx.tok_slot, kv.block_table,
+                                        kv.k_pool, self.H, self.d, self.dr, self.rank, ctx.status, append=writes_cache,
+                                        half_layout=half)
+        o_lat = self.attend(q_rows, kv, ctx)
+        plain = not self.head_gate and out is None and out_mul == 1.0
+        # with a gate (or a factor, or columns to write into) the values leave their product in float32 and are
+        # rounded once, after the gate
+        o = per_head_linear(o_lat.view(n, self.H, self.rank), self.w_uv,
+                            out_dtype=None if plain else torch.float32)             # [n, H, value_dim]
+        if plain:
+            return o.view(n, self.H * self.dv)
+        gate = proj[:, self.g_off:self.g_off + self.H] if self.head_gate else None
+        return kernels.attn_finish(o.view(n, self.H * self.dv), self.H, 1, None, None, out_mul, gate, self.rt.dtype, out=out)
 
     def attend(self, q_rows, kv, ctx):
         """Attention of q_rows [n, H, row] over the cached rows; returns [n, H * kv_rank]."""

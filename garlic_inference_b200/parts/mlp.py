@@ -12,9 +12,11 @@ at load time (one product instead of two); silu and the product are one kernel
 in float32 with a single rounding (upstream rounds after silu and again after
 the product, src/src-cuda/activations/silu.cu:35-67, hadamard.cu:48-67).
 
-`glu_mlp`: down( act(gate(x)) * up(x) ) with `activation` "silu" or "gelu_tanh" (the tanh form of gelu,
-0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))); gate and up packed like SwiGLU's.  With "silu" it runs
-SwiGLU's fused products."""
+`glu_mlp`: down( act(gate(x)) * up(x) ) with `activation` "silu", "gelu_tanh" (the tanh form of gelu,
+0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) or "swish" (z sigmoid(`swish_alpha` z)); gate and up packed
+like SwiGLU's.  Optional limits make it down( act(min(gate x, `gate_max`)) * (clamp(up x, -`up_limit`, `up_limit`)
++ `up_shift`) ).  With "silu" and no limits it runs SwiGLU's fused products.  `pre_output` hands over what goes
+into the down projection, for arrangements that join it with another product."""
 from __future__ import annotations
 
 import torch
@@ -59,17 +61,25 @@ class GluMLP(FeedForward):
         super().__init__(params, load, rt)
         self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
         self.activation = params.get("activation", "silu")
-        if self.activation not in ("silu", "gelu_tanh"):
-            raise ValueError(f"glu_mlp activation {self.activation!r} is neither 'silu' nor 'gelu_tanh'")
+        if self.activation not in kernels.GLU_KINDS:
+            raise ValueError(f"glu_mlp activation {self.activation!r} is none of {sorted(kernels.GLU_KINDS)}")
+        self.unit = kernels.glu_shape(self.activation, params.get("swish_alpha", 1.0), params.get("gate_max"),
+                                      params.get("up_limit"), params.get("up_shift", 0.0))
+        self.plain_silu = self.unit == kernels.glu_shape("silu")
         self.w_gate_up = torch.empty((2 * self.inter, self.hidden), dtype=load.dtype("gate", "up"), device=rt.device)
         load("gate", out=self.w_gate_up[:self.inter])
         load("up", out=self.w_gate_up[self.inter:])
         self.w_down = load("down")
 
+    def pre_output(self, x, ctx, out=None):
+        """unit(gate x, up x): [n, intermediate_size] in the activation type, into `out` (columns of a wider matrix)
+        when given."""
+        if self.plain_silu and out is None:
+            return swiglu_product(x, self.w_gate_up)
+        return kernels.glu(linear(x, self.w_gate_up), self.unit, out=out)
+
     def step(self, x, ctx):
-        if self.activation == "silu":
-            return linear(swiglu_product(x, self.w_gate_up), self.w_down)
-        return linear(kernels.glu(linear(x, self.w_gate_up), self.activation), self.w_down)
+        return linear(self.pre_output(x, ctx), self.w_down)
 
 
 class XieluMLP(FeedForward):

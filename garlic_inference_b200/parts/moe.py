@@ -2,8 +2,16 @@
 
     z = Wr x                                   router logits, float32 (the weight is widened, the product is a
                                                float32 kernel of its own; x may be its 16-bit rounding)
-    the `top` experts with the largest z are chosen; their weights are the softmax over the chosen z alone
-    y = sum_e weight_e Wd_e act(Wu_e x)        act: the square of relu ("relu_squared") or silu; no biases
+    scores "softmax_chosen" (the default): the `top` experts with the largest z are chosen; their weights are the
+                               softmax over the chosen z alone
+    scores "softmax_all":      s = softmax(z) over all experts; the experts lie in `groups` equal groups of
+                               neighbours, a group's score is its largest s, and only the `groups_kept` best groups
+                               stay; the `top` largest s among them are chosen; weights s * `weight_scale`, not
+                               renormalised
+    expert "two_matrix" (the default):  y = sum_e weight_e Wd_e act(Wu_e x), act the square of relu
+                               ("relu_squared") or silu; no biases
+    expert "glu":              y = sum_e weight_e Wd_e unit(Wg_e x, Wu_e x), a gated unit with `activation`,
+                               `swish_alpha`, `gate_max`, `up_limit`, `up_shift` as in `glu_mlp`
 
 The experts' matrices are stacked at load time ([experts, ff, hidden] and [experts, hidden, ff]).  Two ways to
 run them.  A step of a few rows (a decode step; such a step may be recorded, so nothing may come back to the
@@ -38,8 +46,11 @@ class RoutedExperts(FeedForward):
     @classmethod
     def wanted(cls, params):
         hid, ff, E = params["hidden_size"], params["expert_size"], params["n_experts"]
-        w = {"router": TensorWant((E, hid))}
+        # scores over all experts: random routers are made wider, so that random models choose with clear margins
+        w = {"router": TensorWant((E, hid), std_scale=4.0 if params.get("scores") == "softmax_all" else 1.0)}
         for e in range(E):
+            if params.get("expert", "two_matrix") == "glu":
+                w[f"e{e}.gate"] = TensorWant((ff, hid))
             w[f"e{e}.up"], w[f"e{e}.down"] = TensorWant((ff, hid)), TensorWant((hid, ff))
         return w
 
@@ -47,31 +58,65 @@ class RoutedExperts(FeedForward):
         super().__init__(params, load, rt)
         self.hidden, self.ff = int(params["hidden_size"]), int(params["expert_size"])
         self.E, self.top = int(params["n_experts"]), int(params["top"])
-        self.activation = params.get("activation", "relu_squared")
+        self.gated = params.get("expert", "two_matrix") == "glu"
+        if params.get("expert", "two_matrix") not in ("two_matrix", "glu"):
+            raise ValueError(f"expert kind {params['expert']!r} is neither 'two_matrix' nor 'glu'")
+        self.activation = params.get("activation", "silu" if self.gated else "relu_squared")
         if not 0 < self.top <= self.E:
             raise ValueError(f"{self.top} of {self.E} experts")
-        if self.activation not in ("relu_squared", "silu"):
+        if self.gated:
+            # what the kernels take in place of an activation's name: the gated unit's constants
+            self.act = kernels.glu_shape(self.activation, params.get("swish_alpha", 1.0), params.get("gate_max"),
+                                         params.get("up_limit"), params.get("up_shift", 0.0))
+        elif self.activation not in ("relu_squared", "silu"):
             raise ValueError(f"expert activation {self.activation!r} is neither 'relu_squared' nor 'silu'")
+        else:
+            self.act = self.activation
+        self.scores = params.get("scores", "softmax_chosen")
+        if self.scores not in ("softmax_chosen", "softmax_all"):
+            raise ValueError(f"router scores {self.scores!r} are neither 'softmax_chosen' nor 'softmax_all'")
+        self.groups, self.groups_kept = int(params.get("groups", 1)), int(params.get("groups_kept", params.get("groups", 1)))
+        self.weight_scale = float(params.get("weight_scale", 1.0))
+        if self.scores == "softmax_all":
+            per = self.E // max(self.groups, 1)
+            if self.groups <= 0 or self.E % self.groups or not 0 < self.groups_kept <= self.groups or \
+                    self.top > self.groups_kept * per:
+                raise ValueError(f"{self.E} experts in {self.groups} groups of which {self.groups_kept} stay, top {self.top}")
+        elif self.groups != 1 or self.weight_scale != 1.0:
+            raise ValueError("groups of experts and a factor on the weights come with scores 'softmax_all'")
         self.w_router = load("router").to(torch.float32)
-        names = [f"e{e}.up" for e in range(self.E)]
-        dtype = load.dtype(*names, *(f"e{e}.down" for e in range(self.E)))
-        self.w_up = torch.empty((self.E, self.ff, self.hidden), dtype=dtype, device=rt.device)
+        rows = 2 * self.ff if self.gated else self.ff
+        names = [f"e{e}.{n}" for e in range(self.E) for n in (("gate", "up", "down") if self.gated else ("up", "down"))]
+        dtype = load.dtype(*names)
+        self.w_up = torch.empty((self.E, rows, self.hidden), dtype=dtype, device=rt.device)
         self.w_down = torch.empty((self.E, self.hidden, self.ff), dtype=dtype, device=rt.device)
         for e in range(self.E):
-            load(f"e{e}.up", out=self.w_up[e])
+            if self.gated:                            # an expert's gate rows, then its up rows
+                load(f"e{e}.gate", out=self.w_up[e, :self.ff])
+            load(f"e{e}.up", out=self.w_up[e, rows - self.ff:])
             load(f"e{e}.down", out=self.w_down[e])
+
+    def route(self, x):
+        """(chosen experts int32 [n, top], their weights float32 [n, top]) for the rows of x."""
+        logits = kernels.router_logits(x, self.w_router)
+        if self.scores == "softmax_all":
+            return kernels.router_select(logits, self.top, self.groups, self.groups_kept, self.weight_scale)
+        return kernels.router_topk(logits, self.top)
+
+    def _activate(self, z):
+        return kernels.glu(z, self.act) if self.gated else kernels.relu_squared(z)
 
     def step(self, x, ctx):
         n = x.shape[0]
-        logits = kernels.router_logits(x, self.w_router)
-        idx, wt = kernels.router_topk(logits, self.top)
+        idx, wt = self.route(x)
         grouped = self._grouped(x)
-        if n <= ROWWISE_MAX_ROWS or self.activation != "relu_squared" or (ctx.captured and not grouped):
-            return kernels.moe_rowwise(x, self.w_up, self.w_down, idx, wt, self.activation)
+        products = self.gated or self.activation == "relu_squared"     # what the expert-by-expert path computes
+        if n <= ROWWISE_MAX_ROWS or not products or (ctx.captured and not grouped):
+            return kernels.moe_rowwise(x, self.w_up, self.w_down, idx, wt, self.act)
         # expert by expert: the pairs (token, choice) in the order of their experts; `where` is each pair's row
         where, ends, rows = kernels.moe_group(idx, x, self.E)
         if grouped:
-            a = kernels.relu_squared(torch._grouped_mm(rows, self.w_up.transpose(1, 2), offs=ends))
+            a = self._activate(torch._grouped_mm(rows, self.w_up.transpose(1, 2), offs=ends))
             buf = torch._grouped_mm(a, self.w_down.transpose(1, 2), offs=ends)
         else:
             buf = torch.empty((n * self.top, self.hidden), dtype=x.dtype, device=x.device)
@@ -80,7 +125,7 @@ class RoutedExperts(FeedForward):
             for e in range(self.E):
                 c = bounds[e + 1] - bounds[e]
                 if c:
-                    a = kernels.relu_squared(linear(rows[at:at + c], self.w_up[e]))
+                    a = self._activate(linear(rows[at:at + c], self.w_up[e]))
                     buf[at:at + c] = linear(a, self.w_down[e])
                     at += c
         return kernels.moe_combine(buf.contiguous(), where, wt)
