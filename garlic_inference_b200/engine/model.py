@@ -177,6 +177,7 @@ class DecoderModel:
         yield self.embedding
         yield from self.positions.values()
         for b in self.blocks:
+            yield b                                  # an arrangement may hold a joined weight of its own
             for p in (b.mixer, b.feed_forward):
                 if p is not None:
                     yield p

@@ -47,7 +47,7 @@ TINY = {
     # everything, in another order than any other configuration's; layers on an earlier layer's cached rows, among
     # them a chain of readers of two different sources; a rotation of a part of the rotated part
     "mix": dict(vocab=411, width=96, eps=2e-6, emb=9.0, cap=12.0, seed=34, std=0.06, norm_std=0.15,
-                layers=[_with(_latent(4, 16, 8, 24, 48, 40, base=5000.0), _moe(48, 2.0, 8, 2, 4, 2, 2.5)),
+                layers=[_with(_latent(4, 16, 8, 24, 48, 40, base=5000.0), _moe(48, 2.0, 8, 3, 4, 2, 2.5)),
                         _with(_latent(6, 24, 16, 16, 32, 56, dims=12, base=300.0), _dense(128, 1.5)),
                         _with(_latent(2, 32, 8, 40, 48, 24, base=5000.0, kv_from=0), _dense(64, 3.0)),
                         _with(_latent(3, 8, 16, 8, 32, 16, dims=12, base=300.0, kv_from=1)),
