@@ -790,6 +790,220 @@ def study_zogulorn(args, pk) -> int:
     return 0
 
 
+# ---- the Dugopel design beside Fivitar's latent layers and Qwen3 at equal layer sizes -------------------------
+def dugopel_config_dict(width, heads, ff, vocab, n_layers, head_dim=128, kv_rank=512, q_rank=1536, rot_dim=64,
+                        experts=16, top=2, groups=4, keep=2):
+    """`n_layers` layers at sizes of a real model's: a dense feed-forward in the first layer and routed ones (experts
+    of ff / top, so that a token's feed-forward has the dense one's parameters) in the others; every third layer
+    keeps a latent of its own and the two behind it read its cached rows."""
+    def layer(i):
+        mixer = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "kv_rank": kv_rank,
+                 "q_rank": q_rank, "scale": (head_dim + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}}
+        if i >= 1 and (i - 1) % 3:
+            mixer["kv_from"] = 1 + (i - 1) // 3 * 3
+        mlp = {"kind": "dense", "ff": ff, "limit": 7.0} if i == 0 else \
+            {"kind": "moe", "expert": {"ff": max(64, ff // top // 64 * 64), "limit": 7.0},
+             "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups, "keep": keep}}}
+        return {"type": "latent_attention", "mixer": mixer, "mlp": mlp}
+    return {"architecture": "Dugopel", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "layers": [layer(i) for i in range(n_layers)]}
+
+
+def study_dugopel(args, pk) -> int:
+    """Prefill (one prompt of 2,048 tokens) and decode (batches of 1, 8 and 64 with 2,048 cached tokens each) of
+    Dugopel models with random weights, beside a Fivitar model of latent-attention layers alone and a Qwen3 model of
+    the same width, depth, heads and feed-forward parameters, and the design's kernels timed alone beside the
+    closest kernels of the other models.  One JSON line."""
+    import torch
+    from garlic_inference_b200 import LanguageModel, Qwen3Config
+    from garlic_inference_b200.config import DugopelConfig, FivitarConfig
+    from garlic_inference_b200.ops import counters, kernels, linear
+    from garlic_inference_b200.sampling import SamplingParams
+    K, W = min(args.steps, 64), max(min(args.warmup, 8), 3)
+    torch.cuda.set_device(0)
+    greedy = SamplingParams()
+    gen = torch.Generator().manual_seed(0)
+    sizes = [("1b", 2048, 16, 8192, 32000, 7), ("8b", 4096, 32, 18432, 32000, 4)]
+    out = {"study": "dugopel", "dtype": "bfloat16", "data": "synthetic", "steps": K, "warmup": W,
+           "peaks": pk, "models": {}, "kernels": {}}
+
+    def timed(fn, reps=5, warm=3):
+        for _ in range(warm):
+            fn()
+        flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
+        ms = []
+        for _ in range(reps):
+            flush.zero_()                                  # larger than L2: the next run starts cold
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ms.append(a.elapsed_time(b))
+        return statistics.median(ms)
+
+    def run_model(cfg, vocab):
+        per_seq = -(-(CACHED + W + K + 8) // 64) * 64
+        model = LanguageModel.from_random(cfg, seed=0, device=0, dtype="bfloat16", max_tokens=64 * per_seq,
+                                          max_slots=64)
+        eng, sampler = model.engine, model.sampler
+        prompt = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+        res = {"weight_bytes": model.model.weight_bytes()}
+
+        def prefill_once():
+            s = eng.alloc_slot()
+            model.step([(s, prompt(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+            eng.free_slot(s)
+        ms = timed(prefill_once, reps=5, warm=3)
+        res["prefill"] = {"tokens": PREFILL_TOKENS, "ms": round(ms, 3), "tokens_per_s": round(PREFILL_TOKENS / ms * 1e3)}
+        for batch in (1, 8, 64):
+            slots, firsts = [], []
+            for _ in range(batch):
+                s = eng.alloc_slot()
+                firsts.append(sampler.sample(model.step([(s, prompt(CACHED), [CACHED - 1])]), greedy, [0], [0]))
+                slots.append(s)
+            toks = torch.cat(firsts)
+            for _ in range(W):
+                toks = sampler.sample(eng.step_decode_device(slots, toks), greedy, slots, slots)
+            torch.cuda.synchronize()
+            n0 = counters.launches
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(K):
+                toks = sampler.sample(eng.step_decode_device(slots, toks), greedy, slots, slots)
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / K
+            res[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3),
+                                       "launches_per_step": (counters.launches - n0) // K}
+            for s in slots:
+                eng.free_slot(s)
+        eng.check()
+        del model
+        torch.cuda.empty_cache()
+        return res
+
+    for label, width, heads, ff, vocab, n_layers in sizes:
+        dcfg = DugopelConfig.from_dict(dugopel_config_dict(width, heads, ff, vocab, n_layers))
+        fdict = fivitar_config_dict(width, heads, ff * 3 // 2, vocab, 3 * n_layers)      # two matrices: equal parameters
+        fdict["layers"] = [l for l in fdict["layers"] if l["type"] == "latent_attention"]
+        fcfg = FivitarConfig.from_dict(fdict)
+        qcfg = Qwen3Config(hidden_size=width, num_hidden_layers=n_layers, num_attention_heads=heads,
+                           num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=ff,
+                           vocab_size=vocab, max_position_embeddings=CONTEXT * 2)
+        out["models"][label] = {"width": width, "heads": heads, "ff": ff, "layers": n_layers,
+                                "dugopel": run_model(dcfg, vocab), "fivitar_latent": run_model(fcfg, vocab),
+                                "qwen3": run_model(qcfg, vocab)}
+
+    # ---- the kernels alone, at the larger size: 2,048 rows of a prompt, and 8 single tokens ----
+    width, H, d, dr, rank, q_rank, T, page, ffd = 4096, 32, 128, 64, 512, 1536, PREFILL_TOKENS, 64, 18432
+    dev = "cuda"
+    bf = lambda *shape: torch.randn(*shape, device=dev, dtype=torch.bfloat16) * 0.5
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    kern = out["kernels"]
+
+    def note(name, ms, flops=0.0, bytes_=0.0):
+        kern[name] = {"ms": round(ms, 4)}
+        if flops:
+            kern[name]["tflops"] = round(flops / ms / 1e9, 2)
+            kern[name]["of_measured_bf16"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 4)
+        if bytes_:
+            kern[name]["gbs"] = round(bytes_ / ms / 1e6, 1)
+            kern[name]["of_measured_copy"] = round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)
+
+    # the norm beside RMSNorm (one and two pending results), the gated unit beside SwiGLU, 2,048 rows and 8 rows
+    w = bf(width)
+    for n_rows in (T, 8):
+        res, d1, d2 = torch.randn(n_rows, width, device=dev), bf(n_rows, width), bf(n_rows, width)
+        ms = timed(lambda: kernels.add_layernorm(d1, res, w, None, 1e-6, torch.bfloat16, delta2=d2))
+        note(f"add2_layernorm_{n_rows}", ms, bytes_=n_rows * width * (2 + 2 + 4 + 4 + 2))
+        ms = timed(lambda: kernels.add_layernorm(d1, res, w, None, 1e-6, torch.bfloat16))
+        note(f"add_layernorm_{n_rows}", ms, bytes_=n_rows * width * (2 + 4 + 4 + 2))
+        ms = timed(lambda: kernels.add_rmsnorm(d1, res, w, 1e-6, torch.bfloat16))
+        note(f"add_rmsnorm_{n_rows}", ms, bytes_=n_rows * width * (2 + 4 + 4 + 2))
+        gu = bf(n_rows, 2 * ffd)
+        unit = kernels.glu_shape("swish", 1.702, 7.0, 7.0, 1.0)
+        ms = timed(lambda: kernels.glu(gu, unit))
+        note(f"clamped_swish_glu_{n_rows}", ms, bytes_=n_rows * ffd * 6)
+        ms = timed(lambda: kernels.swiglu(gu))
+        note(f"swiglu_{n_rows}", ms, bytes_=n_rows * ffd * 6)
+        x = bf(n_rows, q_rank + 8)
+        ms = timed(lambda: kernels.rmsnorm_rows(x[:, :q_rank], w[:q_rank], 1e-6))
+        note(f"rmsnorm_rows_{n_rows}", ms, bytes_=n_rows * q_rank * 4)
+    # rotation and cache append in the two layouts; attention over the latent rows is the kernel Fivitar's layers run
+    row = rank + dr
+    pool = bf(8 * T // page, 1, page, row)
+    table = torch.arange(8 * T // page, dtype=torch.int32, device=dev).view(8, T // page)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    freq = torch.tensor([10000.0 ** (-2.0 * i / dr) for i in range(dr // 2)], dtype=torch.float32, device=dev)
+    for n_rows, pos, slot in ((T, torch.arange(T, dtype=torch.int32, device=dev), i32([0] * T)),
+                              (8, i32([T - 1] * 8), i32(list(range(8))))):
+        q_src, kv_src, q_lat = bf(n_rows, H * (d + dr)), bf(n_rows, row), bf(n_rows, H, rank)
+        for half in (True, False):
+            ms = timed(lambda: kernels.latent_prepare(q_src, 0, kv_src, 0, q_lat, w[:rank], 1e-6, freq, 1.0, dr, pos, slot,
+                                                      table, pool, H, d, dr, rank, status, half_layout=half))
+            note(f"latent_prepare_{'halves' if half else 'pairs'}_{n_rows}", ms,
+                 bytes_=n_rows * (H * (dr + rank) * 2 + row * 2 + H * row * 2 + row * 2))
+    q8, pos8, slots8 = bf(8, H, row), i32([T - 1] * 8), i32(list(range(8)))
+    ms = timed(lambda: kernels.latent_decode(q8, pool, table, pos8, slots8, 0.07, None, rank, status))
+    note("latent_attention_decode_b8", ms, flops=2.0 * 8 * H * (row + rank) * T, bytes_=8 * T * row * 2)
+    q, rows = bf(T, H, row), pool.view(-1, page, row)[:T // page].reshape(T, row)
+
+    def by_products():
+        for q0 in range(0, T, 1024):
+            scores = torch.mm(q[q0:q0 + 1024].view(1024 * H, row), rows[:q0 + 1024].t(), out_dtype=torch.float32)
+            wts = kernels.causal_sink_softmax(scores, H, q0, 0.07, None, torch.bfloat16)
+            torch.mm(wts, rows[:q0 + 1024, :rank])
+    ms = timed(by_products)
+    note("latent_attention_prefill2048_products", ms, flops=2.0 * H * (row + rank) * T * (T + 1) / 2)
+    # the router beside the other design's, the gated experts beside the two-matrix experts and a dense feed-forward
+    from garlic_inference_b200.parts import Runtime, StepContext, part_class
+    E, top, eff = 16, 2, ffd // 2
+    for n_rows in (8, T):
+        z = torch.randn(n_rows, E, device=dev)
+        ms = timed(lambda: kernels.router_select(z, top, 4, 2, 2.5))
+        note(f"router_select_{n_rows}", ms)
+        ms = timed(lambda: kernels.router_topk(z, top))
+        note(f"router_topk_{n_rows}", ms)
+
+    def experts_part(gated):
+        class Load:
+            def dtype(self, *a):
+                return torch.bfloat16
+
+            def __call__(self, n, out=None):
+                rows_ = eff if gated else eff * 3 // 2
+                shape = (E, width) if n == "router" else ((width, rows_) if n.endswith("down") else (rows_, width))
+                t = bf(*shape) * 0.05
+                return t if out is None else out.copy_(t)
+        params = dict(hidden_size=width, expert_size=eff if gated else eff * 3 // 2, n_experts=E, top=top)
+        if gated:
+            params.update(expert="glu", activation="swish", swish_alpha=1.702, gate_max=7.0, up_limit=7.0, up_shift=1.0,
+                          scores="softmax_all", groups=4, groups_kept=2, weight_scale=2.5)
+        return part_class("routed_experts")(params, Load(), Runtime(torch.bfloat16, torch.device(dev)))
+
+    zero = i32([0])
+    for gated, tag in ((True, "gated_experts"), (False, "two_matrix_experts")):
+        part = experts_part(gated)
+        for n_rows in (1, 8, 64, T):
+            x = bf(n_rows, width)
+            ctx = StepContext(n_rows, zero, zero, zero)
+            ms = timed(lambda: part.step(x, ctx))
+            note(f"{tag}_{n_rows}_rows", ms, flops=6.0 * n_rows * top * eff * width,
+                 bytes_=min(E, n_rows * top) * 3 * eff * width * 2)
+        del part
+        torch.cuda.empty_cache()
+    wgu, wd = bf(2 * ffd, width) * 0.05, bf(width, ffd) * 0.05
+    unit = kernels.glu_shape("swish", 1.702, 7.0, 7.0, 1.0)
+    for n_rows in (1, 8, 64, T):
+        x = bf(n_rows, width)
+        ms = timed(lambda: linear(kernels.glu(linear(x, wgu), unit), wd))
+        note(f"dense_clamped_swish_ff_{n_rows}_rows", ms, flops=6.0 * n_rows * ffd * width, bytes_=3 * ffd * width * 2)
+        ms = timed(lambda: linear(kernels.swiglu(linear(x, wgu)), wd))
+        note(f"dense_swiglu_ff_unfused_{n_rows}_rows", ms, flops=6.0 * n_rows * ffd * width, bytes_=3 * ffd * width * 2)
+    kernels.check_bounded_waits(torch.device("cuda", 0))
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -803,7 +1017,7 @@ def main() -> int:
     ap.add_argument("--write-model", default=None, metavar="DIR",
                     help="with --impl reference: only write the model folder that arm uses (tied head, --layers of the 36) "
                          "to DIR and exit, for running baseline/_ref/bin/reference_runner by hand or under a profiler")
-    ap.add_argument("--study", default=None, choices=["prefill-clocks", "fivitar", "zogulorn"],
+    ap.add_argument("--study", default=None, choices=["prefill-clocks", "fivitar", "zogulorn", "dugopel"],
                     help="prefill-clocks: 40 prompt steps of 2,048 tokens back to back with the clock and the power "
                          "sampled every 20 ms; prints a table and no JSON line.  fivitar: prefill and decode of the "
                          "Fivitar design at two sizes of real layers beside Qwen3 at equal sizes, and the mixers' "
@@ -827,6 +1041,8 @@ def main() -> int:
         return study_fivitar(args, peaks())
     if args.study == "zogulorn":
         return study_zogulorn(args, peaks())
+    if args.study == "dugopel":
+        return study_dugopel(args, peaks())
 
     import torch
     from garlic_inference_b200 import LanguageModel, Qwen3Config

@@ -136,6 +136,26 @@ __device__ __forceinline__ float load_w(const void* w, int w_dtype, int i) {
     return w_dtype == GI_DTYPE_F32 ? ((const float*)w)[i] : __bfloat162float(((const bf16*)w)[i]);
 }
 
+// Four neighbouring elements at a time: float32 as one 16-byte word, bfloat16 as one 8-byte word.
+__device__ __forceinline__ float4 load4_f32(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4_act(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4_act(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4_act(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4_act(bf16* p, float4 v) {
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = o;
+}
+__device__ __forceinline__ float4 load4_w(const void* w, int w_dtype, int c) {
+    return w_dtype == GI_DTYPE_F32 ? load4_f32((const float*)w + c) : load4_act((const bf16*)w + c);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -22,6 +22,7 @@
 //
 // Upstream calls a library product whatever M is (src/src-cuda/mat-ops/gemm/gemm.cu:22-41).
 #include "common.cuh"
+#include "glu.cuh"
 #include <cooperative_groups.h>
 
 namespace cg = cooperative_groups;
@@ -61,13 +62,14 @@ __device__ __forceinline__ void sk_step(float (&acc)[NT][4], const uint4& lo0, c
 }
 
 // GLU: W is [2 I, K], a gate projection in its first I rows and an up projection in its last I.  A CTA then
-// takes R / 2 gate rows and the R / 2 up rows that belong to them, and writes silu(gate) * up, [M, I]
-// bfloat16: each factor rounded to bfloat16 as a stored product would be, then the SwiGLU kernel's float32
-// arithmetic: the product followed by that kernel, up to the order in which a CTA walks K.
+// takes R / 2 gate rows and the R / 2 up rows that belong to them, and writes the gated unit of the two (glu.cuh:
+// silu(gate) * up, or another activation with limits and a shift), [M, I] bfloat16 with rows `ld_out` apart: each
+// factor rounded to bfloat16 as a stored product would be, then the row-wise kernel's float32 arithmetic: the
+// product followed by that kernel, up to the order in which a CTA walks K.
 template <int NT, int WR, int WK, bool GLU>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int out_f32,
-                   int M, int N, int K, int k_slice) {
+                   int M, int N, int K, int k_slice, GluShape unit, long long ld_out) {
     static_assert(WR * WK == SK_WARPS, "8 warps");
     gi_pdl_launch_dependents();
     constexpr int MP = 8 * NT;                   // padded batch
@@ -200,7 +202,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
             const int col = blockIdx.x * half + r;
             if (m < M && col < inter) {
                 const float gf = __bfloat162float(__float2bfloat16_rn(gate)), uf = __bfloat162float(__float2bfloat16_rn(up));
-                reinterpret_cast<bf16*>(out)[(size_t)m * inter + col] = __float2bfloat16_rn(gf / (1.f + expf(-gf)) * uf);
+                reinterpret_cast<bf16*>(out)[(size_t)m * ld_out + col] = __float2bfloat16_rn(glu_unit(gf, uf, unit));
             }
         }
     } else {
@@ -221,7 +223,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
 
 template <int NT, int WR, int WK, bool GLU>
 static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_f32, int M, int N, int K, int n_split,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, GluShape unit, long long ld_out) {
     constexpr int MP = 8 * NT, R = 16 * WR, KC = 64 * WK;
     const size_t smem = (size_t)SK_DEPTH * 4 * SK_THREADS * 16 + (size_t)(WK + 1) * MP * R * sizeof(float);
     if (int rc = gi_reserve_smem((const void*)skinny_gemm_kernel<NT, WR, WK, GLU>, smem, "gi_gemm_skinny_bf16")) return rc;
@@ -240,16 +242,20 @@ static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_f32, i
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = gi_pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, WR, WK, GLU>, x, W, out, out_f32, M, N, K, k_slice);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, WR, WK, GLU>, x, W, out, out_f32, M, N, K, k_slice, unit, ld_out);
     if (e != cudaSuccess) { gi_set_error("gi_gemm_skinny_bf16: launch: %s", cudaGetErrorString(e)); return (int)e; }
     return gi_check_launch("gi_gemm_skinny_bf16");
 }
 
 // n_split: CTAs of a cluster that share K (1 to 8); 0 lets the entry point choose.
 // wide: 0 = 32 rows of W per CTA, 1 = 64 rows, -1 lets the entry point choose.
-// glu: 0 = out[M, N]; 1 = W holds a gate and an up half and out is silu(gate) * up, [M, N / 2] bfloat16.
+// glu: 0 = out[M, N]; 1 = W holds a gate and an up half and out is their gated unit `unit`, [M, N / 2] bfloat16 with
+// rows ld_out apart.
 static int skinny_entry(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K, int n_split,
-                        int wide, int glu, void* stream) {
+                        int wide, int glu, void* stream, GluShape unit = GluShape{0, 1.f, INFINITY, INFINITY, 0.f},
+                        long long ld_out = 0) {
+    if (glu && ld_out == 0) ld_out = N / 2;
+    GI_REQUIRE(!glu || ld_out >= N / 2, "gi_gemm_skinny_glu_bf16: output rows %lld apart hold no %d columns", ld_out, N / 2);
     GI_REQUIRE(M >= 1 && M <= 16, "gi_gemm_skinny_bf16: %d rows; this kernel takes 1 to 16", M);
     GI_REQUIRE(N > 0 && K > 0 && K % 8 == 0, "gi_gemm_skinny_bf16: inner size %d must be a positive multiple of 8", K);
     GI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0), "gi_gemm_skinny_bf16: operands must start on 16 bytes");
@@ -292,8 +298,8 @@ static int skinny_entry(const void* x, const void* W, void* out, int out_dtype, 
     const bf16* wp = (const bf16*)W;
     const int f32 = out_dtype == GI_DTYPE_F32;
     cudaStream_t s = (cudaStream_t)stream;
-#define GI_SK(NT, WR, WK) (glu ? launch_skinny<NT, WR, WK, true>(xp, wp, out, f32, M, N, K, n_split, s) \
-                               : launch_skinny<NT, WR, WK, false>(xp, wp, out, f32, M, N, K, n_split, s))
+#define GI_SK(NT, WR, WK) (glu ? launch_skinny<NT, WR, WK, true>(xp, wp, out, f32, M, N, K, n_split, s, unit, ld_out) \
+                               : launch_skinny<NT, WR, WK, false>(xp, wp, out, f32, M, N, K, n_split, s, unit, ld_out))
     if (M <= 8) return wide ? GI_SK(1, 4, 2) : GI_SK(1, 2, 4);
     return wide ? GI_SK(2, 4, 2) : GI_SK(2, 2, 4);
 #undef GI_SK
@@ -309,4 +315,14 @@ extern "C" int gi_gemm_skinny_bf16(const void* x, const void* W, void* out, int 
 extern "C" int gi_gemm_skinny_swiglu_bf16(const void* x, const void* W, void* out, int M, int two_inter, int K,
                                           int n_split, int wide, void* stream) {
     return skinny_entry(x, W, out, GI_DTYPE_BF16, M, two_inter, K, n_split, wide, 1, stream);
+}
+
+// The same with any gated unit of glu.cuh (activation `kind`, limits, shift) and output rows `ld_out` apart (columns
+// of a wider matrix that another product reads).
+extern "C" int gi_gemm_skinny_glu_bf16(const void* x, const void* W, void* out, long long ld_out, int M, int two_inter, int K,
+                                       int kind, float alpha, float gate_max, float up_limit, float up_shift, int n_split,
+                                       int wide, void* stream) {
+    GI_REQUIRE(kind >= 0 && kind <= 2 && up_limit >= 0.f, "gi_gemm_skinny_glu_bf16: gated unit %d", kind);
+    return skinny_entry(x, W, out, GI_DTYPE_BF16, M, two_inter, K, n_split, wide, 1, stream,
+                        GluShape{kind, alpha, gate_max, up_limit, up_shift}, ld_out);
 }

@@ -22,6 +22,7 @@
 //
 // Upstream calls a library product for every size (src/src-cuda/mat-ops/gemm/gemm.cu:22-41).
 #include "common.cuh"
+#include "glu.cuh"
 
 #include <cuda.h>
 
@@ -139,10 +140,10 @@ __device__ __forceinline__ void tg_store_row(void* out, const uint32_t (&r)[32],
 // 32 columns of silu(gate) * up of one row: both factors rounded to bfloat16 as a stored product would be,
 // then the SwiGLU kernel's float32 arithmetic, rounded once
 __device__ __forceinline__ void tg_store_swiglu(bf16* out, const uint32_t (&g)[32], const uint32_t (&u)[32], int row, int col,
-                                                int M, int inter) {
+                                                int M, int inter, const GluShape& unit, long long ld_out) {
     if (row >= M || col >= inter) return;
-    bf16* dst = out + (size_t)row * inter + col;
-    const bool whole = col + 32 <= inter && (inter & 7) == 0;
+    bf16* dst = out + (size_t)row * ld_out + col;
+    const bool whole = col + 32 <= inter && (ld_out & 7) == 0;
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
         uint32_t packed[4];
@@ -153,7 +154,7 @@ __device__ __forceinline__ void tg_store_swiglu(bf16* out, const uint32_t (&g)[3
             for (int h = 0; h < 2; ++h) {
                 const float gf = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + e + h])));
                 const float uf = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + e + h])));
-                v[h] = gf / (1.f + expf(-gf)) * uf;
+                v[h] = glu_unit(gf, uf, unit);
             }
             __nv_bfloat162 p = __floats2bfloat162_rn(v[0], v[1]);
             packed[e >> 1] = *reinterpret_cast<uint32_t*>(&p);
@@ -353,7 +354,8 @@ __device__ __forceinline__ void tp_cluster_sync() {
 template <int OUT_F32, int SWIGLU>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                         void* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag) {
+                         void* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag,
+                         GluShape unit, long long ld_out) {
     gi_pdl_start();
     extern __shared__ unsigned char tg_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)tg_raw + 1023) & ~(uintptr_t)1023);
@@ -466,7 +468,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     uint32_t g[32], u[32];
                     tg_ld32(acc + c * 32, g);
                     tg_ld32(acc + TP_BN_HALF + c * 32, u);
-                    tg_store_swiglu(reinterpret_cast<bf16*>(out), g, u, row, col0 + c * 32, M, inter);
+                    tg_store_swiglu(reinterpret_cast<bf16*>(out), g, u, row, col0 + c * 32, M, inter, unit, ld_out);
                 }
             } else {
                 const int n0 = (t / m_tiles) * TG_BN;
@@ -580,8 +582,9 @@ extern "C" int gi_gemm_tcgen05_bf16(const void* x, const void* W, void* out, int
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = gi_pdl_enabled() ? 2 : 1;
-        cudaError_t e = f32 ? cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<1, 0>, map_x, map_w, out, M, N, K, error_flag)
-                            : cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<0, 0>, map_x, map_w, out, M, N, K, error_flag);
+        const GluShape none = {0, 1.f, INFINITY, INFINITY, 0.f};
+        cudaError_t e = f32 ? cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<1, 0>, map_x, map_w, out, M, N, K, error_flag, none, 0LL)
+                            : cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<0, 0>, map_x, map_w, out, M, N, K, error_flag, none, 0LL);
         if (e != cudaSuccess) { gi_set_error("gi_gemm_tcgen05_bf16: launch: %s", cudaGetErrorString(e)); return (int)e; }
         return gi_check_launch("gi_gemm_tcgen05_bf16");
     }
@@ -604,13 +607,14 @@ extern "C" int gi_gemm_tcgen05_bf16(const void* x, const void* W, void* out, int
 
 // out[M, I] = silu(x . Wg^T) * (x . Wu^T) for W = [Wg; Wu] of 2 I rows: the gate/up product of a SwiGLU
 // feed-forward with the activation in its epilogue, on pairs of CTAs.  bfloat16 in and out.
-extern "C" int gi_gemm_tcgen05_swiglu_bf16(const void* x, const void* W, void* out, int M, int two_inter, int K,
-                                           int* error_flag, void* stream) {
+static int tcgen05_glu_entry(const void* x, const void* W, void* out, int M, int two_inter, int K, int* error_flag,
+                             void* stream, GluShape unit, long long ld_out) {
     GI_REQUIRE(M > 0 && two_inter > 0 && K > 0, "gi_gemm_tcgen05_swiglu_bf16: sizes must be positive");
     GI_REQUIRE(two_inter % 2 == 0, "gi_gemm_tcgen05_swiglu_bf16: W has %d rows, which cannot be a gate and an up half", two_inter);
     GI_REQUIRE(K % 8 == 0, "gi_gemm_tcgen05_swiglu_bf16: inner size %d is no multiple of 8 (rows must be a multiple of 16 bytes for TMA)", K);
     GI_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)out % 16 == 0),
                "gi_gemm_tcgen05_swiglu_bf16: operands must start on 16 bytes");
+    GI_REQUIRE(ld_out >= two_inter / 2, "gi_gemm_tcgen05_glu_bf16: output rows %lld apart hold no %d columns", ld_out, two_inter / 2);
     GI_REQUIRE(error_flag != nullptr, "gi_gemm_tcgen05_swiglu_bf16: an error flag on the device is required");
     int n_sm = 148;
     {
@@ -646,7 +650,22 @@ extern "C" int gi_gemm_tcgen05_swiglu_bf16(const void* x, const void* W, void* o
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = gi_pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<0, 1>, map_x, map_w, out, M, two_inter, K, error_flag);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<0, 1>, map_x, map_w, out, M, two_inter, K, error_flag, unit, ld_out);
     if (e != cudaSuccess) { gi_set_error("gi_gemm_tcgen05_swiglu_bf16: launch: %s", cudaGetErrorString(e)); return (int)e; }
     return gi_check_launch("gi_gemm_tcgen05_swiglu_bf16");
+}
+
+extern "C" int gi_gemm_tcgen05_swiglu_bf16(const void* x, const void* W, void* out, int M, int two_inter, int K,
+                                           int* error_flag, void* stream) {
+    return tcgen05_glu_entry(x, W, out, M, two_inter, K, error_flag, stream, GluShape{0, 1.f, INFINITY, INFINITY, 0.f},
+                             two_inter / 2);
+}
+
+// The same with any gated unit of glu.cuh (activation `kind`, limits, shift) and output rows `ld_out` apart.
+extern "C" int gi_gemm_tcgen05_glu_bf16(const void* x, const void* W, void* out, long long ld_out, int M, int two_inter, int K,
+                                        int kind, float alpha, float gate_max, float up_limit, float up_shift,
+                                        int* error_flag, void* stream) {
+    GI_REQUIRE(kind >= 0 && kind <= 2 && up_limit >= 0.f, "gi_gemm_tcgen05_glu_bf16: gated unit %d", kind);
+    return tcgen05_glu_entry(x, W, out, M, two_inter, K, error_flag, stream, GluShape{kind, alpha, gate_max, up_limit, up_shift},
+                             ld_out);
 }

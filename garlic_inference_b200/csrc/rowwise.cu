@@ -79,25 +79,6 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restric
 // The same with the row held in registers: one read of the inputs, four elements per thread and load.
 // Taken when dim is a multiple of 4 and at most 8,192; the thread count depends on dim alone.
 #define NORM_VEC_MAX_IT 8
-__device__ __forceinline__ float4 load4_f32(const float* p) { return *reinterpret_cast<const float4*>(p); }
-__device__ __forceinline__ float4 load4_act(const float* p) { return *reinterpret_cast<const float4*>(p); }
-__device__ __forceinline__ float4 load4_act(const bf16* p) {
-    const uint2 v = *reinterpret_cast<const uint2*>(p);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
-    return make_float4(a.x, a.y, b.x, b.y);
-}
-__device__ __forceinline__ void store4_act(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
-__device__ __forceinline__ void store4_act(bf16* p, float4 v) {
-    uint2 o;
-    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v.x, v.y);
-    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v.z, v.w);
-    *reinterpret_cast<uint2*>(p) = o;
-}
-__device__ __forceinline__ float4 load4_w(const void* w, int w_dtype, int c) {
-    return w_dtype == GI_DTYPE_F32 ? load4_f32((const float*)w + c) : load4_act((const bf16*)w + c);
-}
-
 // EARLY_W: the weight is fetched into registers before the wait for the kernel that makes delta (it is
 // nobody's output).  That pays for a few rows, where the kernel is one chain of latencies; for thousands
 // of rows the registers cost more in occupancy than the early fetch gives (13.6 vs 20.1 us at 2,048 rows).

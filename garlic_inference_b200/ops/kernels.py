@@ -838,6 +838,43 @@ def gemm_skinny_swiglu_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, n_split: i
     return out
 
 
+def _glu_out(x, w_gate_up, out):
+    _dense(x, "x", torch.bfloat16), _dense(w_gate_up, "w_gate_up", torch.bfloat16)
+    (m, k), (n2, k2) = x.shape, w_gate_up.shape
+    if k != k2 or n2 % 2:
+        raise KernelError(f"x {tuple(x.shape)} does not fit a gate and an up half {tuple(w_gate_up.shape)}")
+    if out is None:
+        out = torch.empty((m, n2 // 2), dtype=torch.bfloat16, device=x.device)
+    _rows(out, "out", torch.bfloat16)
+    if out.shape != (m, n2 // 2):
+        raise KernelError(f"out {tuple(out.shape)} for a result of {(m, n2 // 2)}")
+    return m, n2, k, out
+
+
+def gemm_skinny_glu_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, unit: tuple, out: Optional[torch.Tensor] = None,
+                         n_split: int = 0, wide: int = -1) -> torch.Tensor:
+    """unit(x . Wg^T, x . Wu^T) for x [M<=16, K] and w_gate_up = [Wg; Wu] with the gated unit (a `glu_shape` tuple) in
+    the last step of the skinny product; `out` may be columns of a wider matrix.  `glu(gemm_skinny_bf16(x,
+    w_gate_up), unit)` up to the rounding of the sums."""
+    l = require_gpu()
+    m, n2, k, out = _glu_out(x, w_gate_up, out)
+    check(l.gi_gemm_skinny_glu_bf16(_ptr(x), _ptr(w_gate_up), _ptr(out), out.stride(0), m, n2, k, *unit, n_split, wide,
+                                    _stream()), l)
+    return out
+
+
+def gemm_tcgen05_glu_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, unit: tuple,
+                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """unit(x . Wg^T, x . Wu^T) with the gated unit (a `glu_shape` tuple) in the epilogue of the tcgen05 product
+    (pairs of CTAs); `out` may be columns of a wider matrix that start on 16 bytes.  The bits of
+    `glu(gemm_tcgen05_bf16(x, w_gate_up), unit)`."""
+    l = require_gpu()
+    m, n2, k, out = _glu_out(x, w_gate_up, out)
+    check(l.gi_gemm_tcgen05_glu_bf16(_ptr(x), _ptr(w_gate_up), _ptr(out), out.stride(0), m, n2, k, *unit,
+                                     _ptr(tcgen05_error_flag(x.device)), _stream()), l)
+    return out
+
+
 _tcgen05_flag: dict = {}
 
 

@@ -114,6 +114,22 @@ def swiglu_product(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     return kernels.swiglu(linear(x, w_gate_up))
 
 
+def glu_product(x: torch.Tensor, w_gate_up: torch.Tensor, unit: tuple, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """unit(x . Wg^T, x . Wu^T) for the packed weight [Wg; Wu] and a gated unit with limits and a shift (a
+    `kernels.glu_shape` tuple), into `out` (columns of a wider matrix) when given: the same choice of kernels as
+    `swiglu_product` makes, with the unit in the product's epilogue for prompts and for decode batches of 1 to 8,
+    and the product of `linear` followed by the row-wise kernel otherwise."""
+    m, k = x.shape
+    fits = (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and k % 8 == 0 and w_gate_up.shape[0] % 2 == 0
+            and x.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0)
+    if fits and FUSED_SWIGLU_MIN_ROWS > 0 and m >= FUSED_SWIGLU_MIN_ROWS and \
+            (out is None or (out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0)):
+        return kernels.gemm_tcgen05_glu_bf16(x, w_gate_up, unit, out=out)
+    if fits and 0 < m <= SKINNY_MAX_ROWS and not (0 < STREAMK_MIN_BYTES <= w_gate_up.numel() * 2):
+        return kernels.gemm_skinny_glu_bf16(x, w_gate_up, unit, out=out)
+    return kernels.glu(linear(x, w_gate_up), unit, out=out)
+
+
 def per_head_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y[n, h, :] = w[h] x[n, h, :] for a weight [heads, out, in] and x [n, heads, in], whose heads and rows may lie
     apart (columns of a wider product's output) while each head's `in` values are dense; returns dense

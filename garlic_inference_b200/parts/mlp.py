@@ -21,7 +21,7 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import kernels, linear, swiglu_product
+from ..ops import glu_product, kernels, linear, swiglu_product
 from ..weights.loader import TensorWant
 from .base import FeedForward, register_part
 
@@ -76,7 +76,7 @@ class GluMLP(FeedForward):
         when given."""
         if self.plain_silu and out is None:
             return swiglu_product(x, self.w_gate_up)
-        return kernels.glu(linear(x, self.w_gate_up), self.unit, out=out)
+        return glu_product(x, self.w_gate_up, self.unit, out=out)
 
     def step(self, x, ctx):
         return linear(self.pre_output(x, ctx), self.w_down)

@@ -255,6 +255,20 @@ def test_gated_unit_with_limits_and_a_shift():
     w2 = w2 * plain.sigmoid(1.702 * w2) * (torch.clamp(gf[:, 32:], -0.5, 0.5) + 1.0)
     torch.testing.assert_close(kernels.glu(gb, kernels.glu_shape("swish", 1.702, 0.5, 0.5, 1.0)).float().cpu(), w2, rtol=1e-2, atol=1e-2)
     torch.testing.assert_close(kernels.glu(gu, "silu").cpu(), g * plain.sigmoid(g) * u, rtol=1e-5, atol=1e-6)
+    # the unit in the epilogue of the two products that have one: a few rows, and a prompt's rows; into columns of a
+    # wider matrix
+    from garlic_inference_b200.ops import glu_product, linear
+    w = (torch.randn(2 * 96, 64, device="cuda") * 0.3).bfloat16()
+    unit = kernels.glu_shape("swish", 1.702, 0.9, 0.9, 1.0)
+    for rows in (3, 8, 700):
+        x = torch.randn(rows, 64, device="cuda").bfloat16()
+        want = kernels.glu(linear(x, w), unit).float().cpu()
+        wide = torch.zeros(rows, 96 + 32, device="cuda", dtype=torch.bfloat16)
+        got = glu_product(x, w, unit, out=wide[:, 32:])
+        torch.testing.assert_close(got.float().cpu(), want, rtol=2e-2, atol=2e-2)
+        assert float(wide[:, :32].abs().max()) == 0.0
+        torch.testing.assert_close(glu_product(x, w, unit).float().cpu(), want, rtol=2e-2, atol=2e-2)
+    kernels.check_bounded_waits(torch.device("cuda", 0))
 
 
 def test_router_over_all_experts_with_groups_and_the_gated_experts():
