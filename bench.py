@@ -817,7 +817,7 @@ def study_dugopel(args, pk) -> int:
     import torch
     from garlic_inference_b200 import LanguageModel, Qwen3Config
     from garlic_inference_b200.config import DugopelConfig, FivitarConfig
-    from garlic_inference_b200.ops import counters, kernels, linear
+    from garlic_inference_b200.ops import counters, glu_product, kernels, linear, swiglu_product
     from garlic_inference_b200.sampling import SamplingParams
     K, W = min(args.steps, 64), max(min(args.warmup, 8), 3)
     torch.cuda.set_device(0)
@@ -995,10 +995,10 @@ def study_dugopel(args, pk) -> int:
     unit = kernels.glu_shape("swish", 1.702, 7.0, 7.0, 1.0)
     for n_rows in (1, 8, 64, T):
         x = bf(n_rows, width)
-        ms = timed(lambda: linear(kernels.glu(linear(x, wgu), unit), wd))
+        ms = timed(lambda: linear(glu_product(x, wgu, unit), wd))
         note(f"dense_clamped_swish_ff_{n_rows}_rows", ms, flops=6.0 * n_rows * ffd * width, bytes_=3 * ffd * width * 2)
-        ms = timed(lambda: linear(kernels.swiglu(linear(x, wgu)), wd))
-        note(f"dense_swiglu_ff_unfused_{n_rows}_rows", ms, flops=6.0 * n_rows * ffd * width, bytes_=3 * ffd * width * 2)
+        ms = timed(lambda: linear(swiglu_product(x, wgu), wd))
+        note(f"dense_swiglu_ff_{n_rows}_rows", ms, flops=6.0 * n_rows * ffd * width, bytes_=3 * ffd * width * 2)
     kernels.check_bounded_waits(torch.device("cuda", 0))
     print(json.dumps(out))
     return 0

@@ -173,13 +173,28 @@ template <> __device__ __forceinline__ float dot_row<float>(const float* __restr
     float s = 0.f;
     if (k % 4 == 0 && (uintptr_t)w % 16 == 0) {
         for (int c = lane * 4; c < k; c += 128) {
-            const float4 v = *reinterpret_cast<const float4*>(w + c);
-            s = fmaf(v.x, x[c], s); s = fmaf(v.y, x[c + 1], s); s = fmaf(v.z, x[c + 2], s); s = fmaf(v.w, x[c + 3], s);
+            const float4 v = *reinterpret_cast<const float4*>(w + c), xv = *reinterpret_cast<const float4*>(x + c);
+            s = fmaf(v.x, xv.x, s); s = fmaf(v.y, xv.y, s); s = fmaf(v.z, xv.z, s); s = fmaf(v.w, xv.w, s);
         }
     } else {
         for (int c = lane; c < k; c += 32) s = fmaf(w[c], x[c], s);
     }
     return warp_sum(s);
+}
+// Eight weights (one 16-byte word) times eight of the token's values, which come out of shared memory as two
+// 16-byte words (eight 4-byte reads at a stride of 32 bytes would meet the same bank from every fourth lane).
+__device__ __forceinline__ float fma8(const uint4& w, const float* __restrict__ x, float s) {
+    const float4 x0 = *reinterpret_cast<const float4*>(x), x1 = *reinterpret_cast<const float4*>(x + 4);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+    float2 f = __bfloat1622float2(p2[0]);
+    s = fmaf(f.x, x0.x, s); s = fmaf(f.y, x0.y, s);
+    f = __bfloat1622float2(p2[1]);
+    s = fmaf(f.x, x0.z, s); s = fmaf(f.y, x0.w, s);
+    f = __bfloat1622float2(p2[2]);
+    s = fmaf(f.x, x1.x, s); s = fmaf(f.y, x1.y, s);
+    f = __bfloat1622float2(p2[3]);
+    s = fmaf(f.x, x1.z, s); s = fmaf(f.y, x1.w, s);
+    return s;
 }
 template <> __device__ __forceinline__ float dot_row<bf16>(const bf16* __restrict__ w, const float* __restrict__ x, int k, int lane) {
     float s = 0.f;
@@ -191,30 +206,51 @@ template <> __device__ __forceinline__ float dot_row<bf16>(const bf16* __restric
 #pragma unroll
             for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(w + c + u * 256);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(p2[i]);
-                    s = fmaf(f.x, x[c + u * 256 + 2 * i], s);
-                    s = fmaf(f.y, x[c + u * 256 + 2 * i + 1], s);
-                }
-            }
+            for (int u = 0; u < 4; ++u) s = fma8(v[u], x + c + u * 256, s);
         }
-        for (; c < k; c += 256) {
-            const uint4 v = *reinterpret_cast<const uint4*>(w + c);
-            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(p2[i]);
-                s = fmaf(f.x, x[c + 2 * i], s);
-                s = fmaf(f.y, x[c + 2 * i + 1], s);
-            }
-        }
+        for (; c < k; c += 256) s = fma8(*reinterpret_cast<const uint4*>(w + c), x + c, s);
     } else {
         for (int c = lane; c < k; c += 32) s = fmaf(__bfloat162float(w[c]), x[c], s);
     }
     return warp_sum(s);
+}
+
+// Two rows of W against the same vector (a gate row and its up row): the vector's values are read once for both.
+template <typename T>
+__device__ __forceinline__ void dot_rows2(const T* __restrict__ w0, const T* __restrict__ w1, const float* __restrict__ x, int k,
+                                          int lane, float& r0, float& r1) {
+    r0 = dot_row<T>(w0, x, k, lane);
+    r1 = dot_row<T>(w1, x, k, lane);
+}
+template <>
+__device__ __forceinline__ void dot_rows2<bf16>(const bf16* __restrict__ w0, const bf16* __restrict__ w1,
+                                                const float* __restrict__ x, int k, int lane, float& r0, float& r1) {
+    if (!(k % 8 == 0 && (uintptr_t)w0 % 16 == 0 && (uintptr_t)w1 % 16 == 0)) {
+        r0 = dot_row<bf16>(w0, x, k, lane);
+        r1 = dot_row<bf16>(w1, x, k, lane);
+        return;
+    }
+    float s0 = 0.f, s1 = 0.f;
+    int c = lane * 8;
+    for (; c + 3 * 256 < k; c += 4 * 256) {             // the same order of additions as dot_row's, row by row
+        uint4 a[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            a[u] = *reinterpret_cast<const uint4*>(w0 + c + u * 256);
+            b[u] = *reinterpret_cast<const uint4*>(w1 + c + u * 256);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            s0 = fma8(a[u], x + c + u * 256, s0);
+            s1 = fma8(b[u], x + c + u * 256, s1);
+        }
+    }
+    for (; c < k; c += 256) {
+        s0 = fma8(*reinterpret_cast<const uint4*>(w0 + c), x + c, s0);
+        s1 = fma8(*reinterpret_cast<const uint4*>(w1 + c), x + c, s1);
+    }
+    r0 = warp_sum(s0);
+    r1 = warp_sum(s1);
 }
 
 // Router logits z[t, e] = sum_c w[e, c] x[t, c] in float32: the weight is float32, the token's vector is widened
@@ -224,7 +260,7 @@ __global__ void __launch_bounds__(256)
 router_logits_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ w, float* __restrict__ z,
                      int E, int hidden) {
     gi_pdl_start();
-    extern __shared__ float xs[];
+    extern __shared__ __align__(16) float xs[];
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) xs[c] = to_f32(x[(size_t)t * ldx + c]);
     __syncthreads();
@@ -270,7 +306,7 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_up_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w_up, const int* __restrict__ idx,
               T* __restrict__ a, int top, int E, int ff, int hidden, int act, int rows_pb, GluShape unit) {
     gi_pdl_start();
-    extern __shared__ float xs[];                   // hidden
+    extern __shared__ __align__(16) float xs[];                   // hidden
     const int tj = blockIdx.x, t = tj / top;
     const int e = idx[tj];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -281,8 +317,8 @@ moe_up_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w_up
         float z;
         if (act == 2) {                             // a gated unit: ff gate rows, then ff up rows
             const T* we = w_up + (size_t)e * 2 * ff * hidden;
-            const float g = ok ? dot_row<T>(we + (size_t)f * hidden, xs, hidden, lane) : 0.f;
-            const float u = ok ? dot_row<T>(we + (size_t)(ff + f) * hidden, xs, hidden, lane) : 0.f;
+            float g = 0.f, u = 0.f;
+            if (ok) dot_rows2<T>(we + (size_t)f * hidden, we + (size_t)(ff + f) * hidden, xs, hidden, lane, g, u);
             z = glu_unit(g, u, unit);
         } else {
             z = ok ? dot_row<T>(w_up + ((size_t)e * ff + f) * hidden, xs, hidden, lane) : 0.f;
@@ -299,7 +335,7 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_down_kernel(const T* __restrict__ a, const T* __restrict__ w_down, const int* __restrict__ idx,
                 T* __restrict__ part, int E, int ff, int hidden, int rows_pb) {
     gi_pdl_start();
-    extern __shared__ float as[];                   // ff
+    extern __shared__ __align__(16) float as[];                   // ff
     const int tj = blockIdx.x;
     const int e = idx[tj];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
