@@ -1021,7 +1021,8 @@ def main() -> int:
                     help="prefill-clocks: 40 prompt steps of 2,048 tokens back to back with the clock and the power "
                          "sampled every 20 ms; prints a table and no JSON line.  fivitar: prefill and decode of the "
                          "Fivitar design at two sizes of real layers beside Qwen3 at equal sizes, and the mixers' "
-                         "kernels alone; one JSON line of its own")
+                         "kernels alone; one JSON line of its own.  zogulorn, dugopel: the same for those designs (dugopel "
+                         "beside Fivitar's latent layers and Qwen3)")
     args = ap.parse_args()
 
     if args.impl == "reference":

@@ -109,6 +109,8 @@ class DugopelConfig:
                 elif kind == "moe":
                     mlp = _typed(mlp, {"kind": str, "expert": dict, "router": dict}, w + ".mlp")
                     mlp["expert"] = _typed(mlp["expert"], {"ff": int, "limit": float}, w + ".mlp.expert")
+                    if isinstance(mlp["router"], dict) and mlp["router"].get("groups") is None:
+                        mlp["router"] = dict(mlp["router"], groups={"count": 1, "keep": 1})     # no groups: one of all
                     mlp["router"] = _typed(mlp["router"], {"experts": int, "top": int, "scale": float, "groups": dict},
                                            w + ".mlp.router")
                     mlp["router"]["groups"] = _typed(mlp["router"]["groups"], {"count": int, "keep": int},

@@ -40,7 +40,7 @@ def _requests(name, lengths, seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["latent", "dense", "moe", "mix", "wide", "ones"])
+@pytest.mark.parametrize("name", ["latent", "dense", "moe", "mix", "wide", "odd", "ones"])
 def test_prompts_decoding_portions_and_batches_agree_with_the_plain_model(name, dtype, model, folder):
     """Every way of cutting the same requests gives the plain logits: whole prompts; all but 40 tokens, then one
     at a time; portions of 2, 7, 33 and 3 tokens; portions with all requests in one batch; unequal requests that
@@ -136,7 +136,7 @@ def test_long_decoding(name, dtype, model, folder):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["moe", "mix", "wide"])
+@pytest.mark.parametrize("name", ["moe", "mix", "wide", "odd"])
 def test_a_dozen_requests_decode_together(name, dtype, model, folder):
     """Twelve unequal requests start together and decode together through a recorded step of 16 rows (four of them
     padding): the routed feed-forward then runs expert by expert inside the recording, the attention kernels see

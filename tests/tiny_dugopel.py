@@ -57,6 +57,10 @@ TINY = {
     "wide": dict(vocab=300, width=128, eps=1e-5, emb=3.0, cap=15.0, seed=35, std=0.05, norm_std=0.1,
                  layers=[_with(_latent(36, 16, 8, 16, 64, 48, scale=0.3), _dense(96, 2.0)),
                          _with(_latent(36, 16, 8, 16, 64, 48, scale=0.3, kv_from=0), _moe(32, 2.0, 16, 3, 8, 3, 1.5))]),
+    # sizes that are multiples of nothing the kernels like: rows of 50, 14, 10 and 6 elements, three heads
+    "odd": dict(vocab=263, width=50, eps=1e-5, emb=2.5, cap=25.0, seed=37, std=0.1, norm_std=0.1,
+                layers=[_with(_latent(3, 6, 6, 10, 14, 10, base=40.0), _moe(18, 1.5, 6, 2, 2, 1, 1.3)),
+                        _with(_latent(3, 10, 6, 6, 14, 22, base=40.0, kv_from=0), _dense(30, 2.5))]),
     # one head, a rotated part of one pair, latents of 8, one expert of one in one group, a second layer on the first's rows
     "ones": dict(vocab=257, width=48, eps=1e-5, emb=1.0, cap=50.0, seed=36, std=0.1, norm_std=0.2,
                  layers=[_with(_latent(1, 8, 2, 8, 8, 8), _moe(24, 5.0, 1, 1, 1, 1, 1.0)),
