@@ -51,11 +51,14 @@ class ScheduleEntry:
     with the same `cache` wrote earlier in the step.  `kv_cache` names another
     cache entry whose paged keys and values this run reads instead of having
     its own (it writes none then), while whatever per-sequence state the layer
-    keeps stays in `cache`."""
+    keeps stays in `cache`.  `offset` = (name, row) names a learned vector of
+    ModelPlan.offsets (row `row` of that table) that joins every token's
+    residual stream right before this run."""
     layer: int
     cache: int
     writes_cache: bool = True
     kv_cache: Optional[int] = None
+    offset: Optional[tuple] = None
 
 
 @dataclass(frozen=True)
@@ -70,6 +73,9 @@ class ModelPlan:
     schedule: tuple[ScheduleEntry, ...]
     final_norm: PartSpec
     head: PartSpec
+    # tables of learned vectors that join the residual stream between layers, by name (`stream_offset` parts);
+    # schedule entries say where
+    offsets: dict[str, PartSpec] = field(default_factory=dict)
 
     def n_cache_entries(self) -> int:
         return 1 + max((e.cache for e in self.schedule), default=-1)

@@ -26,6 +26,8 @@
 //                the n_q query rows of a token are laid out [head][map], the n_kv key heads [key head][map], and
 //                row h = head * maps + map reads key head (head / group) * maps + map and value head head / group,
 //                group = (n_q / maps) / n_vh;
+//   dist_bias    a learned bias per distance and query row, float32 [n_dist, n_q]: the score of key j for the query at
+//                position i gets dist_bias[min(i - j, n_dist - 1), row] added after the scaling;
 //   out_f32      the result is written as float32 whatever the activation type is (a later kernel combines maps).  Upstream hands this to a library
 // (src/src-cuda/attention/fattn.cu:74-86: scale 1/sqrt(head_dim), causal mask
 // aligned to the last key, float32 intermediates).
@@ -59,7 +61,8 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
                     const int* __restrict__ tok_slot, T* __restrict__ out, int n_q, int n_kv, int d,
                     int page_size, int max_pages, int n_pool_pages, int window, float scale,
                     const void* __restrict__ sinks, int sink_dtype, int d_v, int* __restrict__ status,
-                    int chunk, int n_vh, int v_row, int maps, float* __restrict__ out_f32) {
+                    int chunk, int n_vh, int v_row, int maps, float* __restrict__ out_f32,
+                    const float* __restrict__ dist_bias, int n_dist) {
     gi_pdl_start();
     extern __shared__ float smem[];
     const int dw = d > d_v ? d : d_v;        // width of an accumulator row
@@ -118,7 +121,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
                 } else {
                     for (int i = 0; i < d; ++i) a = fmaf(to_f32(k_pool[row + i]), q_s[i], a);
                 }
-                s = a;
+                s = dist_bias ? a + dist_bias[(size_t)min(pos - j, n_dist - 1) * n_q + h] : a;
             }
         }
         const float cmax = warp_max(s);
@@ -171,7 +174,7 @@ static int launch_generic(const void* q, const void* k_pool, const void* v_pool,
                           const int* tok_pos, const int* tok_slot, void* out, int n_tokens, int n_q, int n_kv,
                           int d, int page_size, int max_pages, int n_pool_pages, int window, float scale,
                           const void* sinks, int sink_dtype, int d_v, int* status, int chunk, int n_vh, int v_row,
-                          int maps, float* out_f32, cudaStream_t s) {
+                          int maps, float* out_f32, const float* dist_bias, int n_dist, cudaStream_t s) {
     dim3 grid(n_tokens, n_q);
     const int dw = d > d_v ? d : d_v;
     const size_t smem = ((size_t)d + (size_t)dw * AG_WARPS + 2 * AG_WARPS) * sizeof(float);
@@ -179,7 +182,7 @@ static int launch_generic(const void* q, const void* k_pool, const void* v_pool,
     gi_launch(attn_generic_kernel<T, DPL>, grid, dim3(AG_WARPS * 32), smem, s,                                     \
         (const T*)q, (const T*)k_pool, (const T*)v_pool, block_table, tok_pos, tok_slot, (T*)out,     \
         n_q, n_kv, d, page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status, \
-        chunk, n_vh, v_row, maps, out_f32)
+        chunk, n_vh, v_row, maps, out_f32, dist_bias, n_dist)
     if (dw <= 32) AG_LAUNCH(1);
     else if (dw <= 64) AG_LAUNCH(2);
     else if (dw <= 128) AG_LAUNCH(4);
@@ -198,8 +201,9 @@ extern "C" int gi_attention_masked(const void* q, const void* k_pool, const void
                                    void* out, int n_tokens, int n_q, int n_kv, int d, int page_size,
                                    int max_pages, int n_pool_pages, int window, float scale, const void* sinks,
                                    int sink_dtype, int d_v, int* status, int chunk, int n_vh, int v_row, int maps,
-                                   float* out_f32, void* stream) {
+                                   float* out_f32, const float* dist_bias, int n_dist, void* stream) {
     GI_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && d > 0, "gi_attention_generic: sizes must be positive");
+    GI_REQUIRE(!dist_bias || n_dist > 0, "gi_attention_generic: a distance bias of %d rows", n_dist);
     GI_REQUIRE(maps >= 1 && n_vh >= 1 && n_q % maps == 0 && n_kv == n_vh * maps && (n_q / maps) % n_vh == 0,
                "gi_attention_generic: %d query rows and %d key heads in %d maps over %d value heads", n_q, n_kv, maps, n_vh);
     GI_REQUIRE(d <= 1024, "gi_attention_generic: head_dim %d is beyond 1024", d);
@@ -213,11 +217,11 @@ extern "C" int gi_attention_masked(const void* q, const void* k_pool, const void
     if (act_dtype == GI_DTYPE_F32)
         return launch_generic<float>(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, n_tokens, n_q, n_kv, d,
                                      page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status,
-                                     chunk, n_vh, v_row, maps, out_f32, s);
+                                     chunk, n_vh, v_row, maps, out_f32, dist_bias, n_dist, s);
     if (act_dtype == GI_DTYPE_BF16)
         return launch_generic<bf16>(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, n_tokens, n_q, n_kv, d,
                                     page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status,
-                                    chunk, n_vh, v_row, maps, out_f32, s);
+                                    chunk, n_vh, v_row, maps, out_f32, dist_bias, n_dist, s);
     GI_REQUIRE(false, "gi_attention_generic: activation dtype %d", act_dtype);
 }
 
@@ -230,5 +234,5 @@ extern "C" int gi_attention_generic(const void* q, const void* k_pool, const voi
     GI_REQUIRE(d_v > 0 && d_v <= d, "gi_attention_generic: %d value columns of rows of %d", d_v, d);
     return gi_attention_masked(q, k_pool, v_pool, act_dtype, block_table, tok_pos, tok_slot, out, n_tokens, n_q, n_kv, d,
                                page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status, 0, n_kv, d,
-                               1, nullptr, stream);
+                               1, nullptr, nullptr, 0, stream);
 }

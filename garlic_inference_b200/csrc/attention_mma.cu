@@ -72,10 +72,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // query sees only the keys of its own chunk of positions (chunks counted from position 0).
 // maps > 1: one launch serves all maps; the grid's head axis is then maps times as long and block y belongs to map
 // y / heads, which adds map * D to q_o, map to k_add and map * DV to o_o.
+// sinks: float32 [n_q], a score per query head that takes part in the softmax's denominator and has no value.
+// dist_bias: float32 [n_dist, n_q], added to the scaled score of key j for the query at position i at row
+// min(i - j, n_dist - 1), column the query head.  Both are null for mixers without them.
 struct AttnLayout {
     long long q_ts, q_hs, q_o, o_ts, o_hs, o_o;
     int n_kh, k_mul, k_add, chunk, maps;
+    const float* sinks;
+    const float* dist_bias;
+    int n_dist;
 };
+#define AT_LOG2E 1.4426950408889634f
 
 // Element offset of row j of a sequence inside a pool (for key/value head kvh), or -1 when j is not below
 // key_end or its page is not mapped.  No branch around the table read, so that a thread's reads for
@@ -301,7 +308,10 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
                     const int j = key0 + nt * 8 + 2 * t + (e & 1);
                     const int p = p_row[e >> 1];
                     const bool ok = j <= p && (window <= 0 || j > p - window) && j >= c_row[e >> 1];
-                    s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
+                    float sc = s[nt][e] * scale_log2;
+                    if (lay.dist_bias && ok)
+                        sc = fmaf(__ldg(lay.dist_bias + (size_t)min(p - j, lay.n_dist - 1) * n_q + h), AT_LOG2E, sc);
+                    s[nt][e] = ok ? sc : -INFINITY;
                 }
             }
             uint32_t pf[AT_BN / 16][4];
@@ -314,6 +324,16 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
     for (int hh = 0; hh < 2; ++hh) {
         l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 1);
         l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 2);
+    }
+    if (lay.sinks) {                                        // the sink joins the denominator: a key without a value
+        const float s0 = __ldg(lay.sinks + h) * AT_LOG2E;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const float M = fmaxf(m[hh], s0), f = exp2f(m[hh] - M);      // f = 0 for a row that saw no key
+            l[hh] = l[hh] * f + exp2f(s0 - M);
+#pragma unroll
+            for (int dt = 0; dt < DV / 8; ++dt) { o[dt][hh * 2] *= f; o[dt][hh * 2 + 1] *= f; }
+        }
     }
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
@@ -438,7 +458,12 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int j = key0 + nt * 8 + 2 * t + (e & 1);
-                    s[nt][e] = (j <= pos && j >= lo) ? s[nt][e] * scale_log2 : -INFINITY;
+                    const bool ok = j <= pos && j >= lo;
+                    float sc = s[nt][e] * scale_log2;
+                    if (lay.dist_bias && ok && g + (e >> 1) * 8 < grp)
+                        sc = fmaf(__ldg(lay.dist_bias + (size_t)min(pos - j, lay.n_dist - 1) * n_q + kvh * grp + g + (e >> 1) * 8),
+                                  AT_LOG2E, sc);
+                    s[nt][e] = ok ? sc : -INFINITY;
                 }
             uint32_t pf[1][4];
             softmax_update<DV, 2>(s, m, l, o, pf);
@@ -493,7 +518,8 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
 template <int D>
 __global__ void __launch_bounds__(128)
 decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
-                      int n_splits, int n_q, long long o_ts, long long o_hs, long long o_o, int maps) {
+                      int n_splits, int n_q, long long o_ts, long long o_hs, long long o_o, int maps,
+                      const float* __restrict__ sinks) {
     gi_pdl_start();
     const size_t row = blockIdx.x;                               // (sequence * maps + map) * n_q + head
     // where the row's result goes: dense rows, or (n_q > 0) sequence * o_ts + head * o_hs + o_o + map * D
@@ -502,8 +528,11 @@ decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict_
     const float* ml = part_ml + row * n_splits * 2;
     float M = -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
+    // a sink (n_q > 0 only): one more slice with sum 1 and no output
+    const float s0 = sinks ? __ldg(sinks + row % n_q) * AT_LOG2E : -INFINITY;
+    M = fmaxf(M, s0);
     for (int dim = threadIdx.x; dim < D; dim += blockDim.x) {
-        float acc = 0.f, L = 0.f;
+        float acc = 0.f, L = sinks ? exp2f(s0 - M) : 0.f;
         if (M != -INFINITY) {
             for (int s = 0; s < n_splits; ++s) {
                 const float ms = ml[2 * s];
@@ -578,6 +607,7 @@ static AttnLayout plain_layout(int n_q, int d, int dv) {
     lay.q_ts = (long long)n_q * d; lay.q_hs = d; lay.q_o = 0;
     lay.o_ts = (long long)n_q * dv; lay.o_hs = dv; lay.o_o = 0;
     lay.n_kh = 0; lay.k_mul = 1; lay.k_add = 0; lay.chunk = 0; lay.maps = 1;
+    lay.sinks = lay.dist_bias = nullptr; lay.n_dist = 0;
     return lay;
 }
 
@@ -587,6 +617,7 @@ static AttnLayout map_layout(int n_q, int n_kv, int d, int dv, int maps, int chu
     lay.q_ts = (long long)n_q * maps * d; lay.q_hs = (long long)maps * d; lay.q_o = 0;
     lay.o_ts = (long long)n_q * maps * dv; lay.o_hs = (long long)maps * dv; lay.o_o = 0;
     lay.n_kh = n_kv * maps; lay.k_mul = maps; lay.k_add = 0; lay.chunk = chunk; lay.maps = maps;
+    lay.sinks = lay.dist_bias = nullptr; lay.n_dist = 0;
     return lay;
 }
 
@@ -627,10 +658,15 @@ extern "C" int gi_attention_prefill_bf16(const void* q, const void* k_pool, cons
 extern "C" int gi_attention_prefill_masked_bf16(const void* q, const void* k_pool, const void* v_pool,
                                                 const int* block_table, const int* tiles, int n_tiles, void* out, int n_q,
                                                 int n_kv, int d, int dv, int page_size, int max_pages, int n_pool_pages,
-                                                int window, int chunk, int maps, float scale, void* stream) {
+                                                int window, int chunk, int maps, float scale, const float* sinks,
+                                                const float* dist_bias, int n_dist, void* stream) {
     GI_REQUIRE(maps >= 1 && chunk >= 0, "gi_attention_prefill_masked_bf16: %d maps, chunk %d", maps, chunk);
+    GI_REQUIRE((!sinks && !dist_bias) || maps == 1, "gi_attention_prefill_masked_bf16: sinks and distance biases come with one map per head");
+    GI_REQUIRE(!dist_bias || n_dist > 0, "gi_attention_prefill_masked_bf16: a distance bias of %d rows", n_dist);
+    AttnLayout lay = map_layout(n_q, n_kv, d, dv, maps, chunk);
+    lay.sinks = sinks; lay.dist_bias = dist_bias; lay.n_dist = n_dist;
     return prefill_bf16_layout(q, k_pool, v_pool, block_table, tiles, n_tiles, out, n_q, n_kv, d, dv, page_size,
-                               max_pages, n_pool_pages, window, scale, map_layout(n_q, n_kv, d, dv, maps, chunk), stream);
+                               max_pages, n_pool_pages, window, scale, lay, stream);
 }
 
 static int decode_bf16_layout(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
@@ -656,7 +692,7 @@ static int decode_bf16_layout(const void* q, const void* k_pool, const void* v_p
             (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, tok_pos, tok_slot, part_o,  \
             part_ml, n_q, n_kv, page_size, max_pages, n_pool_pages, window, scale_log2, n_splits, lay);        \
         gi_launch(decode_combine_kernel<DV>, dim3(n_seqs * n_q * lay.maps), dim3(DV < 128 ? (DV < 32 ? 32 : DV) : 128), 0, (cudaStream_t)stream,  \
-            part_o, part_ml, (bf16*)out, n_splits, cq, lay.o_ts, lay.o_hs, lay.o_o, lay.maps);                 \
+            part_o, part_ml, (bf16*)out, n_splits, cq, lay.o_ts, lay.o_hs, lay.o_o, lay.maps, cq ? lay.sinks : nullptr); \
     }
     AT_DISPATCH_DD(d, dv, CALL)
 #undef CALL
@@ -680,11 +716,16 @@ extern "C" int gi_attention_decode_masked_bf16(const void* q, const void* k_pool
                                                const int* block_table, const int* tok_pos, const int* tok_slot, void* out,
                                                float* part_o, float* part_ml, int n_seqs, int n_q, int n_kv, int d, int dv,
                                                int page_size, int max_pages, int n_pool_pages, int window, int chunk,
-                                               int maps, float scale, int n_splits, void* stream) {
+                                               int maps, float scale, int n_splits, const float* sinks,
+                                               const float* dist_bias, int n_dist, void* stream) {
     GI_REQUIRE(maps >= 1 && chunk >= 0, "gi_attention_decode_masked_bf16: %d maps, chunk %d", maps, chunk);
+    GI_REQUIRE((!sinks && !dist_bias) || maps == 1, "gi_attention_decode_masked_bf16: sinks and distance biases come with one map per head");
+    GI_REQUIRE(!dist_bias || n_dist > 0, "gi_attention_decode_masked_bf16: a distance bias of %d rows", n_dist);
+    AttnLayout lay = map_layout(n_q, n_kv, d, dv, maps, chunk);
+    lay.sinks = sinks; lay.dist_bias = dist_bias; lay.n_dist = n_dist;
     return decode_bf16_layout(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, part_o, part_ml, n_seqs,
                               n_q, n_kv, d, dv, page_size, max_pages, n_pool_pages, window, scale, n_splits,
-                              map_layout(n_q, n_kv, d, dv, maps, chunk), true, stream);
+                              lay, true, stream);
 }
 
 // Merges the slices' partial results of a split-KV decode kernel (this file's or the tcgen05 one):
@@ -697,7 +738,7 @@ extern "C" int gi_attention_decode_combine(const float* part_o, const float* par
     if (rows == 0) return 0;
 #define CALL(DD)                                                                                                 \
     gi_launch(decode_combine_kernel<DD>, dim3(rows), dim3(DD < 128 ? (DD < 32 ? 32 : DD) : 128), 0, (cudaStream_t)stream, \
-              part_o, part_ml, (bf16*)out, n_splits, 0, 0LL, 0LL, 0LL, 1);
+              part_o, part_ml, (bf16*)out, n_splits, 0, 0LL, 0LL, 0LL, 1, (const float*)nullptr);
     AT_DISPATCH_D(d, CALL)
 #undef CALL
     return gi_check_launch("gi_attention_decode_combine");

@@ -8,7 +8,11 @@
 //                     inputs are columns of one wider matrix (a packed projection, or the output of the short
 //                     convolutions, which is float32 whatever the activation type is).  With n_rot = 0 nothing
 //                     turns; with k_off < 0 the layer has no keys and values of its own (it reads another layer's)
-//                     and only the queries are written.
+//                     and only the queries are written.  Before the rotation, optionally: a bias per column (`bias`,
+//                     laid out [queries | keys | values] like the columns themselves); an RMS norm of all query
+//                     columns of the token at once and another of all its key columns, each with a weight per column
+//                     (`norm_w`, [queries | keys]; x / sqrt(mean(x^2) + eps) * w); and a factor on the queries that
+//                     grows with the position p, 1 + temp_coef ln(floor((p + 1) / temp_every) + 1).  All float32.
 //   gi_attn_finish    per token and head: o = a_1 - lam a_2 for mixers with two softmax maps per head (lam one
 //                     number on the device), o = a_1 otherwise; optionally o / sqrt(mean(o^2) + eps); times a
 //                     constant; times sigmoid(gate logit of the head); rounded once into the activation type.
@@ -25,13 +29,39 @@ __global__ void attn_prepare_kernel(const TI* __restrict__ src, long long ld, in
                                     const int* __restrict__ tok_pos, const int* __restrict__ tok_slot,
                                     const int* __restrict__ block_table, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                     T* __restrict__ q_out, int n_qh, int n_kh, int n_vh, int d, int dv, int page_size,
-                                    int max_pages, int n_pool_pages, int append, int* __restrict__ status) {
+                                    int max_pages, int n_pool_pages, int append, int* __restrict__ status,
+                                    const void* __restrict__ bias, int bias_dtype, const void* __restrict__ norm_w,
+                                    int norm_dtype, float norm_eps, float temp_coef, int temp_every) {
     gi_pdl_start();
     extern __shared__ float cs[];                 // cos [n_rot/2], sin [n_rot/2]
+    __shared__ float red[33];
     const int t = blockIdx.x;
     const int slot = tok_slot[t], pos = tok_pos[t];
     const TI* row = src + (size_t)t * ld;
     const int pairs = n_rot / 2;
+    const int nq = n_qh * d, nk = k_off >= 0 ? n_kh * d : 0;
+    // element i of the token's queries (i < nq) or keys (i - nq) as float32, with its bias
+    auto raw = [&](int i) {
+        const float x = to_f32(row[i < nq ? q_off + i : k_off + (i - nq)]);
+        return bias ? x + load_w(bias, bias_dtype, i) : x;
+    };
+    float q_mul = 1.f, k_mul = 1.f;
+    if (norm_w) {
+        float sq = 0.f, sk = 0.f;
+        for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float x = raw(i); sq = fmaf(x, x, sq); }
+        for (int i = nq + threadIdx.x; i < nq + nk; i += blockDim.x) { const float x = raw(i); sk = fmaf(x, x, sk); }
+        sq = block_sum(sq, red);
+        __syncthreads();
+        sk = block_sum(sk, red);
+        q_mul = 1.f / sqrtf(sq / (float)nq + norm_eps);
+        if (nk) k_mul = 1.f / sqrtf(sk / (float)nk + norm_eps);
+    }
+    if (temp_every > 0) q_mul *= 1.f + temp_coef * logf((float)((max(pos, 0) + 1) / temp_every) + 1.f);
+    // the same element as the attention reads it: normed, weighted, and (queries) times the position's factor
+    auto val = [&](int i) {
+        const float x = raw(i) * (i < nq ? q_mul : k_mul);
+        return norm_w ? x * load_w(norm_w, norm_dtype, i) : x;
+    };
     for (int r = threadIdx.x; r < pairs; r += blockDim.x) {
         float s, c;
         sincosf((float)pos * freq[r], &s, &c);
@@ -59,8 +89,7 @@ __global__ void attn_prepare_kernel(const TI* __restrict__ src, long long ld, in
         const int h = i / pairs, r = i - h * pairs;
         const int a = half_layout ? r : 2 * r, b = half_layout ? r + pairs : 2 * r + 1;
         const bool is_q = h < n_qh;
-        const TI* in = row + (is_q ? q_off + h * d : k_off + (h - n_qh) * d);
-        const float u = to_f32(in[a]), v = to_f32(in[b]);
+        const float u = val(h * d + a), v = val(h * d + b);
         const float c = cs[r], s = cs[pairs + r];
         const float ua = u * c - v * s, vb = v * c + u * s;
         if (is_q) {
@@ -78,14 +107,16 @@ __global__ void attn_prepare_kernel(const TI* __restrict__ src, long long ld, in
     for (int i = threadIdx.x; i < heads * rest; i += blockDim.x) {
         const int h = i / rest, c = n_rot + (i - h * rest);
         const bool is_q = h < n_qh;
-        const float x = to_f32(row[(is_q ? q_off + h * d : k_off + (h - n_qh) * d) + c]);
+        const float x = val(h * d + c);
         if (is_q) q_out[((size_t)t * n_qh + h) * d + c] = from_f32<T>(x);
         else if (page >= 0) k_pool[((page * n_kh + (h - n_qh)) * page_size + in_page) * d + c] = from_f32<T>(x);
     }
     if (page >= 0) {
         for (int i = threadIdx.x; i < n_vh * dv; i += blockDim.x) {
             const int h = i / dv, c = i - h * dv;
-            v_pool[((page * n_vh + h) * page_size + in_page) * dv + c] = from_f32<T>(to_f32(row[v_off + i]));
+            const float x = to_f32(row[v_off + i]);
+            v_pool[((page * n_vh + h) * page_size + in_page) * dv + c] =
+                from_f32<T>(bias ? x + load_w(bias, bias_dtype, nq + nk + i) : x);
         }
     }
 }
@@ -94,8 +125,11 @@ extern "C" int gi_attn_prepare(const void* src, int src_dtype, long long ld, int
                                const float* freq, int n_rot, int half_layout, const int* tok_pos, const int* tok_slot,
                                const int* block_table, void* k_pool, void* v_pool, void* q_out, int act_dtype,
                                int n_tokens, int n_qh, int n_kh, int n_vh, int d, int dv, int page_size, int max_pages,
-                               int n_pool_pages, int append, int* status, void* stream) {
+                               int n_pool_pages, int append, int* status, const void* bias, int bias_dtype,
+                               const void* norm_w, int norm_dtype, float norm_eps, float temp_coef, int temp_every,
+                               void* stream) {
     GI_REQUIRE(n_tokens >= 0 && n_qh > 0 && d > 0 && dv > 0, "gi_attn_prepare: sizes must be positive");
+    GI_REQUIRE(temp_every >= 0 && (!norm_w || norm_eps > 0.f), "gi_attn_prepare: the queries' factor and the norm's eps");
     GI_REQUIRE(n_rot >= 0 && n_rot % 2 == 0 && n_rot <= d, "gi_attn_prepare: %d rotated dimensions of heads of %d", n_rot, d);
     GI_REQUIRE(k_off < 0 || (n_kh > 0 && n_vh > 0 && page_size > 0 && max_pages > 0), "gi_attn_prepare: key/value sizes");
     if (n_tokens == 0) return 0;
@@ -106,7 +140,8 @@ extern "C" int gi_attn_prepare(const void* src, int src_dtype, long long ld, int
 #define AP_LAUNCH(TI, T)                                                                                             \
     gi_launch(attn_prepare_kernel<TI, T>, dim3(n_tokens), dim3(threads), smem, s, (const TI*)src, ld, q_off, k_off,   \
               v_off, freq, n_rot, half_layout, tok_pos, tok_slot, block_table, (T*)k_pool, (T*)v_pool, (T*)q_out,     \
-              n_qh, n_kh, n_vh, d, dv, page_size, max_pages, n_pool_pages, append, status)
+              n_qh, n_kh, n_vh, d, dv, page_size, max_pages, n_pool_pages, append, status, bias, bias_dtype, norm_w,     \
+              norm_dtype, norm_eps, temp_coef, temp_every)
     if (src_dtype == GI_DTYPE_F32 && act_dtype == GI_DTYPE_F32) AP_LAUNCH(float, float);
     else if (src_dtype == GI_DTYPE_F32 && act_dtype == GI_DTYPE_BF16) AP_LAUNCH(float, bf16);
     else if (src_dtype == GI_DTYPE_BF16 && act_dtype == GI_DTYPE_BF16) AP_LAUNCH(bf16, bf16);

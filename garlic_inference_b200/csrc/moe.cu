@@ -7,13 +7,17 @@
 //   gi_router_select   per token: scores = softmax of its float32 router logits over all experts; the experts lie in
 //                      `groups` equal groups of neighbours, a group's score is its best expert's, and only the
 //                      `keep` best groups stay; the `top` largest scores among them are chosen (ties: the lower
-//                      index), in falling order; the weights are those scores times `scale`, not renormalised
+//                      index), in falling order; the weights are those scores times `scale`, not renormalised.
+//                      Options: scores = sigmoid of each logit instead of the softmax; a correction per expert added
+//                      to the scores that choose (groups and experts) but not to the weights; a group's score the
+//                      sum of its `group_top` best choosing scores; the weights divided by their sum (+ 1e-20)
+//                      before the factor.  Experts of groups that do not stay cannot be chosen, whatever their scores.
 //   gi_moe_up          a[t, j, :] = act( W_up[e_tj] x_t )          act: the square of relu (0) or silu (1); or (2)
 //                      a gated unit: W_up[e] holds ff gate rows and then ff up rows, a = unit(gate, up) (glu.cuh)
 //   gi_moe_down        part[t, j, :] = W_down[e_tj] a[t, j, :]
 //   gi_moe_group       the (token, choice) pairs in the order of their experts: each pair's row, each expert's last
 //                      row, and the tokens' vectors gathered into that order (a stable counting sort)
-//   gi_moe_combine     y[t, :] = sum_j w_tj buf[where[t, j], :]   in the router's order of j: over gi_moe_down's
+//   gi_moe_combine     y[t, :] = (add[t, :] +) sum_j w_tj buf[where[t, j], :]   in the router's order of j: over gi_moe_down's
 //                      rows (where = none: row t top + j), or over rows that a grouped product wrote expert by expert
 //
 // gi_moe_up and gi_moe_down read only the chosen experts' weights and take the expert of a row from device
@@ -77,30 +81,41 @@ extern "C" int gi_router_topk(const float* logits, long long ld, int E, int top,
 #define RS_WARPS 4
 __global__ void __launch_bounds__(RS_WARPS * 32)
 router_select_kernel(const float* __restrict__ logits, long long ld, int E, int top, int groups, int keep, float scale,
-                     int* __restrict__ idx_out, float* __restrict__ w_out, int n_rows) {
+                     int* __restrict__ idx_out, float* __restrict__ w_out, int n_rows, int sigmoid_scores,
+                     const float* __restrict__ correction, int group_top, int normalize) {
     gi_pdl_start();
-    extern __shared__ float rs_smem[];                   // per warp: E scores, then `groups` group scores
+    extern __shared__ float rs_smem[];                   // per warp: E scores that choose, E plain scores, `groups` group scores
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * RS_WARPS + warp;
     if (r >= n_rows) return;
-    float* sc = rs_smem + (size_t)warp * (E + groups);
-    float* gs = sc + E;
+    float* sc = rs_smem + (size_t)warp * (2 * E + groups);
+    float* plain = sc + E;
+    float* gs = plain + E;
     const float* z = logits + (size_t)r * ld;
-    float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - m); sc[e] = p; sum += p; }
-    sum = warp_sum(sum);
+    if (sigmoid_scores) {
+        for (int e = lane; e < E; e += 32) plain[e] = 1.f / (1.f + expf(-z[e]));
+    } else {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - m); plain[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < E; e += 32) plain[e] = plain[e] / sum;
+    }
     __syncwarp();
-    for (int e = lane; e < E; e += 32) sc[e] = sc[e] / sum;
+    for (int e = lane; e < E; e += 32) sc[e] = correction ? plain[e] + correction[e] : plain[e];
     __syncwarp();
     const int per = E / groups;
     if (keep < groups) {
         for (int g = lane; g < groups; g += 32) {
-            float b = -INFINITY;
-            for (int k = 0; k < per; ++k) b = fmaxf(b, sc[g * per + k]);
-            gs[g] = b;
+            float b = -INFINITY, b2 = -INFINITY;         // the group's best and second best
+            for (int k = 0; k < per; ++k) {
+                const float v = sc[g * per + k];
+                if (v > b) { b2 = b; b = v; } else if (v > b2) b2 = v;
+            }
+            gs[g] = group_top >= 2 && per >= 2 ? b + b2 : b;
         }
         __syncwarp();
         // the `keep` best groups in the order (score falling, index rising); the others' experts leave the choice
@@ -148,21 +163,34 @@ router_select_kernel(const float* __restrict__ logits, long long ld, int E, int 
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
         }
-        if (lane == 0) { idx_out[(size_t)r * top + j] = bi; w_out[(size_t)r * top + j] = best * scale; }
+        if (lane == 0) { idx_out[(size_t)r * top + j] = bi; w_out[(size_t)r * top + j] = plain[bi]; }
         prev_v = best; prev_i = bi;
+    }
+    __syncwarp();
+    if (lane == 0) {
+        float mul = scale;
+        if (normalize) {
+            float sum = 0.f;
+            for (int j = 0; j < top; ++j) sum += w_out[(size_t)r * top + j];
+            mul = scale / (sum + 1e-20f);
+        }
+        for (int j = 0; j < top; ++j) w_out[(size_t)r * top + j] *= mul;
     }
 }
 
 extern "C" int gi_router_select(const float* logits, long long ld, int E, int top, int groups, int keep, float scale,
-                                int* idx_out, float* w_out, int n_rows, void* stream) {
+                                int* idx_out, float* w_out, int n_rows, int sigmoid_scores, const float* correction,
+                                int group_top, int normalize, void* stream) {
+    GI_REQUIRE(group_top == 1 || group_top == 2, "gi_router_select: a group is judged by its best or its two best experts");
     GI_REQUIRE(n_rows >= 0 && E > 0 && ld >= E, "gi_router_select: sizes");
     GI_REQUIRE(groups > 0 && E % groups == 0 && keep > 0 && keep <= groups, "gi_router_select: %d experts in %d groups of which %d stay", E, groups, keep);
     GI_REQUIRE(top > 0 && top <= keep * (E / groups), "gi_router_select: %d of the %d experts that stay", top, keep * (E / groups));
-    const size_t smem = (size_t)RS_WARPS * (E + groups) * sizeof(float);
+    const size_t smem = (size_t)RS_WARPS * (2 * E + groups) * sizeof(float);
     GI_REQUIRE(smem <= 48 * 1024, "gi_router_select: %d experts do not fit shared memory", E);
     if (n_rows == 0) return 0;
     gi_launch(router_select_kernel, dim3((n_rows + RS_WARPS - 1) / RS_WARPS), dim3(RS_WARPS * 32), smem, (cudaStream_t)stream,
-              logits, ld, E, top, groups, keep, scale, idx_out, w_out, n_rows);
+              logits, ld, E, top, groups, keep, scale, idx_out, w_out, n_rows, sigmoid_scores, correction, group_top,
+              normalize);
     return gi_check_launch("gi_router_select");
 }
 
@@ -514,11 +542,11 @@ extern "C" int gi_moe_group(const int* idx, const void* x, long long ldx, int ac
 // ------------------------------------------------------------------ the weighted sum over rows written expert by expert
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ buf, const int* __restrict__ where, const float* __restrict__ wt,
-                                   T* __restrict__ y, int top, int hidden) {
+                                   T* __restrict__ y, int top, int hidden, const T* __restrict__ add) {
     gi_pdl_start();
     const size_t t = blockIdx.x;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hidden; c += gridDim.y * blockDim.x) {
-        float acc = 0.f;
+        float acc = add ? to_f32(add[t * hidden + c]) : 0.f;      // what every token gets besides (a shared expert)
         for (int j = 0; j < top; ++j)
             acc = fmaf(wt[t * top + j], to_f32(buf[(size_t)(where ? where[t * top + j] : (int)(t * top + j)) * hidden + c]), acc);
         y[t * hidden + c] = from_f32<T>(acc);
@@ -526,15 +554,15 @@ __global__ void moe_combine_kernel(const T* __restrict__ buf, const int* __restr
 }
 
 extern "C" int gi_moe_combine(const void* buf, const int* where, const float* wt, void* y, int act_dtype, int n_rows,
-                              int top, int hidden, void* stream) {
+                              int top, int hidden, const void* add, void* stream) {
     GI_REQUIRE(n_rows >= 0 && top > 0 && hidden > 0, "gi_moe_combine: sizes");
     if (n_rows == 0) return 0;
     dim3 grid(n_rows, (hidden + 1023) / 1024);
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32)
-        gi_launch(moe_combine_kernel<float>, grid, dim3(256), 0, s, (const float*)buf, where, wt, (float*)y, top, hidden);
+        gi_launch(moe_combine_kernel<float>, grid, dim3(256), 0, s, (const float*)buf, where, wt, (float*)y, top, hidden, (const float*)add);
     else if (act_dtype == GI_DTYPE_BF16)
-        gi_launch(moe_combine_kernel<bf16>, grid, dim3(256), 0, s, (const bf16*)buf, where, wt, (bf16*)y, top, hidden);
+        gi_launch(moe_combine_kernel<bf16>, grid, dim3(256), 0, s, (const bf16*)buf, where, wt, (bf16*)y, top, hidden, (const bf16*)add);
     else
         GI_REQUIRE(false, "gi_moe_combine: activation dtype %d", act_dtype);
     return gi_check_launch("gi_moe_combine");

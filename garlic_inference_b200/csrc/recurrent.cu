@@ -47,18 +47,22 @@ template <typename T>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long ldx, int C, const void* __restrict__ taps,
                                         int taps_dtype, int K, const float* __restrict__ state, long long state_stride,
                                         const int* __restrict__ tok_slot, float* __restrict__ out, int act,
-                                        float* __restrict__ state_out) {
+                                        float* __restrict__ state_out, const void* __restrict__ in_bias,
+                                        const void* __restrict__ out_bias, int bias_dtype) {
     gi_pdl_start();
     const int r = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
     const int slot = tok_slot[r];
     const int have = slot < 0 ? 0 : rows_before(tok_slot, r, slot, K - 1);
-    float acc = 0.f;
+    // a bias on the inputs belongs to the tokens (what the state holds has it already, and before a sequence's
+    // first token there are zeros, not biases); a bias on the outputs starts the sum
+    const float bin = in_bias ? load_w(in_bias, bias_dtype, c) : 0.f;
+    float acc = out_bias ? load_w(out_bias, bias_dtype, c) : 0.f;
     float seen[CONV_MAX_TAPS];                       // the inputs, oldest first (for the state when it is renewed here)
     for (int j = K - 1; j >= 0; --j) {               // oldest input first, whatever its source
         float xv = 0.f;
-        if (j <= have) xv = to_f32(x[(size_t)(r - j) * ldx + c]);
+        if (j <= have) xv = to_f32(x[(size_t)(r - j) * ldx + c]) + bin;
         else if (slot >= 0) xv = state[(size_t)slot * state_stride + (size_t)(K - 1 + have - j) * C + c];
         seen[K - 1 - j] = xv;
         acc = fmaf(load_w(taps, taps_dtype, c * K + (K - 1 - j)), xv, acc);
@@ -73,7 +77,8 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long ldx, 
 template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ x, long long ldx, int C, int K,
                                          float* __restrict__ state, long long state_stride,
-                                         const int* __restrict__ tok_slot, int n_rows) {
+                                         const int* __restrict__ tok_slot, int n_rows,
+                                         const void* __restrict__ in_bias, int bias_dtype) {
     gi_pdl_start();
     const int r = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -81,20 +86,24 @@ __global__ void conv_state_update_kernel(const T* __restrict__ x, long long ldx,
     const int slot = tok_slot[r];
     if (slot < 0 || (r + 1 < n_rows && tok_slot[r + 1] == slot)) return;      // only a sequence's last row acts
     const int have = rows_before(tok_slot, r, slot, K - 1);
+    const float bin = in_bias ? load_w(in_bias, bias_dtype, c) : 0.f;
     float* st = state + (size_t)slot * state_stride;
     float vals[CONV_MAX_TAPS];
     for (int m = 0; m < K - 1; ++m) {
         const int j = K - 2 - m;                     // how far before the last row
-        vals[m] = j <= have ? to_f32(x[(size_t)(r - j) * ldx + c]) : st[(size_t)(K - 1 + have - j) * C + c];
+        vals[m] = j <= have ? to_f32(x[(size_t)(r - j) * ldx + c]) + bin : st[(size_t)(K - 1 + have - j) * C + c];
     }
     for (int m = 0; m < K - 1; ++m) st[(size_t)m * C + c] = vals[m];
 }
 
 // `act` 1: silu of the filter's sum; 0: the sum itself.  update_state 2: the filter and the renewal of the state in
 // one launch, for steps in which no two rows belong to one sequence (the caller's promise).
-extern "C" int gi_causal_conv(const void* x, long long ldx, int act_dtype, int C, const void* taps, int taps_dtype,
-                              int K, float* state, long long state_stride, const int* tok_slot, float* out,
-                              int n_rows, int update_state, int act, void* stream) {
+// `in_bias` (one per channel, added to every input of a token) and `out_bias` (one per channel, added to the sum)
+// may be null; they share `bias_dtype`.
+extern "C" int gi_causal_conv_biased(const void* x, long long ldx, int act_dtype, int C, const void* taps, int taps_dtype,
+                                     int K, float* state, long long state_stride, const int* tok_slot, float* out,
+                                     int n_rows, int update_state, int act, const void* in_bias, const void* out_bias,
+                                     int bias_dtype, void* stream) {
     GI_REQUIRE(n_rows >= 0 && C > 0 && K >= 1 && K <= CONV_MAX_TAPS, "gi_causal_conv_silu: %d channels, %d taps (1 to %d)",
                C, K, CONV_MAX_TAPS);
     GI_REQUIRE(ldx >= C && state_stride >= (long long)(K - 1) * C, "gi_causal_conv_silu: strides shorter than the rows");
@@ -103,15 +112,22 @@ extern "C" int gi_causal_conv(const void* x, long long ldx, int act_dtype, int C
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_rows, (C + 127) / 128);
     if (act_dtype == GI_DTYPE_F32) {
-        if (update_state != 1) gi_launch(causal_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out, act, update_state == 2 && K > 1 ? state : (float*)nullptr);
-        else if (K > 1) gi_launch(conv_state_update_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, K, state, state_stride, tok_slot, n_rows);
+        if (update_state != 1) gi_launch(causal_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out, act, update_state == 2 && K > 1 ? state : (float*)nullptr, in_bias, out_bias, bias_dtype);
+        else if (K > 1) gi_launch(conv_state_update_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, K, state, state_stride, tok_slot, n_rows, in_bias, bias_dtype);
     } else if (act_dtype == GI_DTYPE_BF16) {
-        if (update_state != 1) gi_launch(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out, act, update_state == 2 && K > 1 ? state : (float*)nullptr);
-        else if (K > 1) gi_launch(conv_state_update_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, K, state, state_stride, tok_slot, n_rows);
+        if (update_state != 1) gi_launch(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out, act, update_state == 2 && K > 1 ? state : (float*)nullptr, in_bias, out_bias, bias_dtype);
+        else if (K > 1) gi_launch(conv_state_update_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, K, state, state_stride, tok_slot, n_rows, in_bias, bias_dtype);
     } else {
         GI_REQUIRE(false, "gi_causal_conv_silu: activation dtype %d", act_dtype);
     }
     return gi_check_launch("gi_causal_conv_silu");
+}
+
+extern "C" int gi_causal_conv(const void* x, long long ldx, int act_dtype, int C, const void* taps, int taps_dtype,
+                              int K, float* state, long long state_stride, const int* tok_slot, float* out,
+                              int n_rows, int update_state, int act, void* stream) {
+    return gi_causal_conv_biased(x, ldx, act_dtype, C, taps, taps_dtype, K, state, state_stride, tok_slot, out, n_rows,
+                                 update_state, act, nullptr, nullptr, GI_DTYPE_F32, stream);
 }
 
 extern "C" int gi_causal_conv_silu(const void* x, long long ldx, int act_dtype, int C, const void* taps, int taps_dtype,

@@ -52,7 +52,8 @@ extern "C" int gi_embedding(const int* ids, const void* table, int table_dtype, 
 template <typename T>
 __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restrict__ residual,
                                    const void* __restrict__ weight, int w_dtype, T* __restrict__ out,
-                                   const int* __restrict__ rows, int dim, float eps, int write_residual) {
+                                   const int* __restrict__ rows, int dim, float eps, int write_residual,
+                                   const void* __restrict__ offset, int off_dtype) {
     gi_pdl_start();
     __shared__ float red[33];
     const int r = blockIdx.x;
@@ -63,7 +64,8 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restric
     for (int c = threadIdx.x; c < dim; c += blockDim.x) {
         float s = res[c];
         if (del) s += to_f32(del[c]);
-        if (write_residual && del) res[c] = s;
+        if (offset) s += load_w(offset, off_dtype, c);      // a vector that joins every row of the stream here
+        if (write_residual && (del || offset)) res[c] = s;
         ss += s * s;
     }
     ss = block_sum(ss, red);
@@ -71,7 +73,10 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restric
     T* o = out + (size_t)r * dim;
     for (int c = threadIdx.x; c < dim; c += blockDim.x) {
         float s = res[c];
-        if (del && !write_residual) s += to_f32(del[c]);
+        if (!write_residual) {
+            if (del) s += to_f32(del[c]);
+            if (offset) s += load_w(offset, off_dtype, c);
+        }
         o[c] = from_f32<T>(s * inv * load_w(weight, w_dtype, c));
     }
 }
@@ -85,7 +90,8 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restric
 template <typename T, int EARLY_W>
 __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ delta, float* __restrict__ residual,
                                        const void* __restrict__ weight, int w_dtype, T* __restrict__ out,
-                                       const int* __restrict__ rows, int dim, float eps, int write_residual) {
+                                       const int* __restrict__ rows, int dim, float eps, int write_residual,
+                                       const void* __restrict__ offset, int off_dtype) {
     gi_pdl_launch_dependents();
     __shared__ float red[33];
     const int r = blockIdx.x;
@@ -118,8 +124,12 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ delta, float* __res
             if (del) {
                 const float4 d4 = load4_act(del + c);
                 s.x += d4.x; s.y += d4.y; s.z += d4.z; s.w += d4.w;
-                if (write_residual) *reinterpret_cast<float4*>(res + c) = s;
             }
+            if (offset) {
+                const float4 o4 = load4_w(offset, off_dtype, c);
+                s.x += o4.x; s.y += o4.y; s.z += o4.z; s.w += o4.w;
+            }
+            if (write_residual && (del || offset)) *reinterpret_cast<float4*>(res + c) = s;
             v[it] = s;
             ss += s.x * s.x;                     // the same order of additions whatever the batch is
             ss += s.y * s.y;
@@ -142,20 +152,21 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ delta, float* __res
 
 extern "C" int gi_add_rmsnorm(const void* delta, float* residual, const void* weight, int w_dtype,
                               void* out, int act_dtype, const int* rows, int n_rows, int dim,
-                              float eps, int write_residual, void* stream) {
+                              float eps, int write_residual, const void* offset, int off_dtype, void* stream) {
     GI_REQUIRE(n_rows >= 0 && dim > 0, "gi_add_rmsnorm: sizes must be positive");
+    GI_REQUIRE(!offset || off_dtype == GI_DTYPE_F32 || off_dtype == GI_DTYPE_BF16, "gi_add_rmsnorm: offset dtype %d", off_dtype);
     GI_REQUIRE(w_dtype == GI_DTYPE_F32 || w_dtype == GI_DTYPE_BF16, "gi_add_rmsnorm: weight dtype %d", w_dtype);
     GI_REQUIRE(!(rows && write_residual), "gi_add_rmsnorm: gathered rows cannot write the residual back");
     if (n_rows == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const bool aligned = ((uintptr_t)residual % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
-                         ((uintptr_t)delta % 16 == 0);
+                         ((uintptr_t)delta % 16 == 0) && ((uintptr_t)offset % 16 == 0);
     if (dim % 4 == 0 && dim <= 256 * 4 * NORM_VEC_MAX_IT && aligned) {
         int threads = ((dim / 4 + 31) / 32) * 32;
         threads = threads > 256 ? 256 : threads;
         const bool early = n_rows <= 256;
 #define LAUNCH_NORM(T, E) gi_launch(add_rmsnorm_vec_kernel<T, E>, dim3(n_rows), dim3(threads), 0, s, (const T*)delta, residual, \
-                                    weight, w_dtype, (T*)out, rows, dim, eps, write_residual)
+                                    weight, w_dtype, (T*)out, rows, dim, eps, write_residual, offset, off_dtype)
         if (act_dtype == GI_DTYPE_F32) { if (early) LAUNCH_NORM(float, 1); else LAUNCH_NORM(float, 0); }
         else if (act_dtype == GI_DTYPE_BF16) { if (early) LAUNCH_NORM(bf16, 1); else LAUNCH_NORM(bf16, 0); }
 #undef LAUNCH_NORM
@@ -166,10 +177,10 @@ extern "C" int gi_add_rmsnorm(const void* delta, float* residual, const void* we
     const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : (dim >= 128 ? 128 : 32));
     if (act_dtype == GI_DTYPE_F32)
         gi_launch(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, (const float*)delta, residual, weight, w_dtype,
-                                                             (float*)out, rows, dim, eps, write_residual);
+                                                             (float*)out, rows, dim, eps, write_residual, offset, off_dtype);
     else if (act_dtype == GI_DTYPE_BF16)
         gi_launch(add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, (const bf16*)delta, residual, weight, w_dtype,
-                                                            (bf16*)out, rows, dim, eps, write_residual);
+                                                            (bf16*)out, rows, dim, eps, write_residual, offset, off_dtype);
     else
         GI_REQUIRE(false, "gi_add_rmsnorm: activation dtype %d", act_dtype);
     return gi_check_launch("gi_add_rmsnorm");
@@ -197,6 +208,28 @@ extern "C" int gi_residual_add(const void* delta, int act_dtype, float* residual
     else
         GI_REQUIRE(false, "gi_residual_add: activation dtype %d", act_dtype);
     return gi_check_launch("gi_residual_add");
+}
+
+// residual[r, c] += vec[c] for every row: a learned vector that joins the whole stream (arrangements whose first
+// norm does not take it along).
+__global__ void residual_add_row_kernel(const void* __restrict__ vec, int vec_dtype, float* __restrict__ residual,
+                                        size_t n, int dim) {
+    gi_pdl_start();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) residual[i] += load_w(vec, vec_dtype, (int)(i % dim));
+}
+
+extern "C" int gi_residual_add_row(const void* vec, int vec_dtype, float* residual, long long n_rows, int dim, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && dim > 0, "gi_residual_add_row: sizes");
+    GI_REQUIRE(vec_dtype == GI_DTYPE_F32 || vec_dtype == GI_DTYPE_BF16, "gi_residual_add_row: vector dtype %d", vec_dtype);
+    const long long n = n_rows * dim;
+    if (n == 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((n + threads - 1) / threads < 4096 ? (n + threads - 1) / threads : 4096);
+    gi_launch(residual_add_row_kernel, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, vec, vec_dtype, residual,
+              (size_t)n, dim);
+    return gi_check_launch("gi_residual_add_row");
 }
 
 // ------------------------------------------------------------------- SwiGLU

@@ -28,7 +28,7 @@ def _part_wants(spec: PartSpec) -> dict[str, TensorWant]:
 
 
 def plan_part_specs(plan: ModelPlan) -> list[PartSpec]:
-    specs = [plan.embedding, *plan.positions.values()]
+    specs = [plan.embedding, *plan.positions.values(), *plan.offsets.values()]
     for layer in plan.layers:
         specs += [layer.mixer, *([layer.feed_forward] if layer.feed_forward is not None else []),
                   *layer.norms.values(), *layer.gates.values()]
@@ -79,6 +79,7 @@ class DecoderModel:
 
         self.embedding = make(plan.embedding)
         self.positions = {name: make(spec) for name, spec in plan.positions.items()}
+        self.offsets = {name: make(spec) for name, spec in plan.offsets.items()}
         self.blocks = []
         for i, layer in enumerate(plan.layers):
             if layer.position is not None and layer.position not in self.positions:
@@ -96,13 +97,15 @@ class DecoderModel:
         for e in self.schedule:
             if not 0 <= e.layer < len(self.blocks):
                 raise IndexError(f"the schedule names layer {e.layer}; the plan has {len(self.blocks)}")
+            if e.offset is not None and e.offset[0] not in self.offsets:
+                raise KeyError(f"the schedule names the offset table {e.offset[0]!r}; the plan has {sorted(self.offsets)}")
         self.vocab_size, self.hidden_size, self.max_positions = plan.vocab_size, plan.hidden_size, plan.max_positions
 
     @property
     def graph_safe(self) -> bool:
         """True if every part allows a decode step to be recorded into a CUDA graph."""
-        return all(p.graph_safe for p in (self.embedding, *self.positions.values(), *self.blocks,
-                                          self.final_norm, self.head))
+        return all(p.graph_safe for p in (self.embedding, *self.positions.values(), *self.offsets.values(),
+                                          *self.blocks, self.final_norm, self.head))
 
     def cache_requirements(self) -> list:
         """What each cache entry has to hold; entries shared by several runs must agree."""
@@ -148,13 +151,18 @@ class DecoderModel:
         ctx.residual_act = None                      # a context may be run again (recording a decode step)
         ctx.delta_scale = None
         ctx.delta_extra = None
+        ctx.stream_offset = None
         residual = self.embedding.step(ctx)
         for pos in self.positions.values():
             pos.on_embedding(residual, ctx)
         delta = None
         for e in self.schedule:
+            if e.offset is not None:                 # the block's first norm takes it along, or the block adds it
+                ctx.stream_offset = self.offsets[e.offset[0]].row(e.offset[1])
             delta = self.blocks[e.layer].step(delta, residual, ctx, cache.view(e.cache, e.kv_cache),
                                               e.writes_cache and e.kv_cache is None)
+            if ctx.stream_offset is not None:
+                raise RuntimeError(f"block '{self.plan.layers[e.layer].block}' left the schedule's offset unapplied")
         if want_rows is None or want_rows.numel() == 0:
             return None
         scaled = {"delta_scale": ctx.delta_scale} if ctx.delta_scale is not None and delta is not None else {}
@@ -176,6 +184,7 @@ class DecoderModel:
     def _all_parts(self):
         yield self.embedding
         yield from self.positions.values()
+        yield from self.offsets.values()
         for b in self.blocks:
             yield b                                  # an arrangement may hold a joined weight of its own
             for p in (b.mixer, b.feed_forward):

@@ -64,9 +64,11 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor
 
 def add_rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor, eps: float,
                 act_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
-                write_residual: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """normed = rmsnorm(residual (+ delta)) * weight in `act_dtype`; with `write_residual` the
-    float32 sum goes back into `residual`.  `rows` (int32) picks input rows (then nothing is written back)."""
+                write_residual: bool = True, out: Optional[torch.Tensor] = None,
+                offset: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """normed = rmsnorm(residual (+ delta) (+ offset)) * weight in `act_dtype`; with `write_residual` the
+    float32 sum goes back into `residual`.  `rows` (int32) picks input rows (then nothing is written back).
+    `offset` [dim]: a vector that joins every row."""
     l = require_gpu()
     _dense(residual, "residual", torch.float32)
     _dense(weight, "weight")
@@ -82,11 +84,16 @@ def add_rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: t
         n_rows, write_residual = rows.numel(), False
     else:
         n_rows = residual.numel() // dim
+    if offset is not None:
+        _dense(offset, "offset")
+        if offset.numel() != dim:
+            raise KernelError(f"an offset of {offset.numel()} elements for rows of {dim}")
     if out is None:
         out = torch.empty((n_rows, dim), dtype=act_dtype, device=residual.device)
     _dense(out, "out", act_dtype)
     check(l.gi_add_rmsnorm(_ptr(delta), _ptr(residual), _ptr(weight), code(weight.dtype), _ptr(out),
-                           code(act_dtype), _ptr(rows), n_rows, dim, float(eps), int(write_residual), _stream()), l)
+                           code(act_dtype), _ptr(rows), n_rows, dim, float(eps), int(write_residual), _ptr(offset),
+                           code(offset.dtype) if offset is not None else F32, _stream()), l)
     return out
 
 
@@ -144,6 +151,16 @@ def residual_add(delta: torch.Tensor, residual: torch.Tensor) -> None:
     if delta.shape != residual.shape:
         raise KernelError(f"delta {tuple(delta.shape)} and residual {tuple(residual.shape)} differ")
     check(l.gi_residual_add(_ptr(delta), code(delta.dtype), _ptr(residual), residual.numel(), _stream()), l)
+
+
+def residual_add_row(vec: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual[r, :] += vec for every row (float32 sums)."""
+    l = require_gpu()
+    _dense(vec, "vec"), _dense(residual, "residual", torch.float32)
+    dim = residual.shape[-1]
+    if vec.numel() != dim:
+        raise KernelError(f"a vector of {vec.numel()} elements for rows of {dim}")
+    check(l.gi_residual_add_row(_ptr(vec), code(vec.dtype), _ptr(residual), residual.numel() // dim, dim, _stream()), l)
 
 
 def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -254,9 +271,12 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
 
 def attention_masked(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                      tok_pos: torch.Tensor, tok_slot: torch.Tensor, scale: float, status: torch.Tensor, window: int = 0,
-                     chunk: int = 0, maps: int = 1, out_float32: bool = False) -> torch.Tensor:
+                     chunk: int = 0, maps: int = 1, out_float32: bool = False, sinks: Optional[torch.Tensor] = None,
+                     dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Exact-order attention of q [n, rows, d] over keys [pages, key heads, page, d] and values [pages, value
-    heads, page, dv] of their own shape.  `chunk` > 0: a query sees the keys of its own chunk of positions only
+    heads, page, dv] of their own shape.  `sinks` [rows]: a score per query row that joins the softmax's denominator
+    without a value.  `dist_bias` float32 [n_dist, rows]: added to the scaled score of key j for the query at
+    position i at row min(i - j, n_dist - 1).  `chunk` > 0: a query sees the keys of its own chunk of positions only
     (chunks counted from position 0).  `maps` > 1: the rows of a token are [head][map] and the key heads [key
     head][map]; every map is a softmax of its own over the head's values.  Returns [n, rows * dv], float32 when
     asked, else q's type."""
@@ -269,22 +289,43 @@ def attention_masked(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
         raise KernelError(f"cache pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit queries of {d}")
     for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (block_table, "block_table"), (status, "status")):
         _dense(t, name, torch.int32)
+    n_dist = _check_sinks_bias(sinks, dist_bias, n_q)
     out = torch.empty((n, n_q * dv), dtype=torch.float32 if out_float32 else q.dtype, device=q.device)
     check(l.gi_attention_masked(_ptr(q), _ptr(k_pool), _ptr(v_pool), code(q.dtype), _ptr(block_table), _ptr(tok_pos),
                                 _ptr(tok_slot), None if out_float32 else _ptr(out), n, n_q, n_kv, d, page_size,
-                                block_table.shape[1], n_pages, int(window or 0), float(scale), None, F32, dv,
+                                block_table.shape[1], n_pages, int(window or 0), float(scale), _ptr(sinks), F32, dv,
                                 _ptr(status), int(chunk or 0), n_vh, dv, int(maps), _ptr(out) if out_float32 else None,
-                                _stream()), l)
+                                _ptr(dist_bias), n_dist, _stream()), l)
     return out
+
+
+def _check_sinks_bias(sinks: Optional[torch.Tensor], dist_bias: Optional[torch.Tensor], rows: int) -> int:
+    """Checks a sink vector [rows] and a distance-bias table [n_dist, rows] (both float32); returns n_dist."""
+    if sinks is not None:
+        _dense(sinks, "sinks", torch.float32)
+        if sinks.numel() != rows:
+            raise KernelError(f"{sinks.numel()} sinks for {rows} query rows")
+    if dist_bias is None:
+        return 0
+    _dense(dist_bias, "dist_bias", torch.float32)
+    if dist_bias.dim() != 2 or dist_bias.shape[1] != rows or dist_bias.shape[0] < 1:
+        raise KernelError(f"a distance bias {tuple(dist_bias.shape)} for {rows} query rows")
+    return int(dist_bias.shape[0])
 
 
 def attn_prepare(src: torch.Tensor, q_off: int, k_off: int, v_off: int, freq: Optional[torch.Tensor], n_rot: int,
                  half_layout: bool, tok_pos: torch.Tensor, tok_slot: torch.Tensor, block_table: Optional[torch.Tensor],
                  k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], n_q_rows: int, d: int,
-                 act_dtype: torch.dtype, status: torch.Tensor, append: bool = True) -> torch.Tensor:
+                 act_dtype: torch.dtype, status: torch.Tensor, append: bool = True,
+                 bias: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
+                 temp_coef: float = 0.0, temp_every: int = 0) -> torch.Tensor:
     """Between projections (or convolutions) and attention: the queries of `src` [n, >= columns] at `q_off` come
     back as [n, n_q_rows, d] in `act_dtype`, their first `n_rot` dimensions turned by position x `freq`; with
-    `k_off` >= 0 the keys (turned alike) and values at `k_off` / `v_off` go into the token's cache page."""
+    `k_off` >= 0 the keys (turned alike) and values at `k_off` / `v_off` go into the token's cache page.  Before the
+    rotation, in float32: `bias` (a number per column, [queries | keys | values]) is added; with `norm_weight`
+    ([queries | keys]) all of a token's query columns are divided by their root mean square (eps inside the root)
+    and multiplied by their weights, and its key columns likewise; with `temp_every` > 0 the queries at position p
+    are multiplied by 1 + temp_coef ln(floor((p + 1) / temp_every) + 1)."""
     l = require_gpu()
     _rows(src, "src")
     n = src.shape[0]
@@ -302,12 +343,23 @@ def attn_prepare(src: torch.Tensor, q_off: int, k_off: int, v_off: int, freq: Op
         max_pages = block_table.shape[1]
         if pool_d != d:
             raise KernelError(f"key pool rows of {pool_d} for heads of {d}")
+    cols_qk = n_q_rows * d + (n_kh * d if k_off >= 0 else 0)
+    if bias is not None:
+        _dense(bias, "bias")
+        if bias.numel() != cols_qk + (n_vh * dv if k_off >= 0 else 0):
+            raise KernelError(f"a bias of {bias.numel()} elements for {cols_qk} query and key columns and the values")
+    if norm_weight is not None:
+        _dense(norm_weight, "norm_weight")
+        if norm_weight.numel() != cols_qk or not norm_eps > 0:
+            raise KernelError(f"a norm weight of {norm_weight.numel()} elements for {cols_qk} query and key columns, eps {norm_eps}")
     q_out = torch.empty((n, n_q_rows, d), dtype=act_dtype, device=src.device)
     check(l.gi_attn_prepare(_ptr(src), code(src.dtype), src.stride(0), q_off, k_off, v_off, _ptr(freq) if n_rot else None,
                             n_rot, int(half_layout), _ptr(tok_pos), _ptr(tok_slot), _ptr(block_table) if k_off >= 0 else None,
                             _ptr(k_pool) if k_off >= 0 else None, _ptr(v_pool) if k_off >= 0 else None, _ptr(q_out),
                             code(act_dtype), n, n_q_rows, n_kh, n_vh, d, max(dv, 1), page_size, max_pages, n_pages,
-                            int(append), _ptr(status), _stream()), l)
+                            int(append), _ptr(status), _ptr(bias), code(bias.dtype) if bias is not None else F32,
+                            _ptr(norm_weight), code(norm_weight.dtype) if norm_weight is not None else F32,
+                            float(norm_eps), float(temp_coef), int(temp_every), _stream()), l)
     return q_out
 
 
@@ -450,23 +502,30 @@ def router_topk(logits: torch.Tensor, top: int):
     return idx, wt
 
 
-def router_select(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float):
-    """Scores = softmax of the float32 `logits` over all experts; of `groups` equal groups of neighbouring experts the
-    `keep` with the largest best score stay; (the `top` experts with the largest scores among those int32 [n, top] in
-    falling order, their scores times `scale` float32): no renormalisation."""
+def router_select(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float, sigmoid: bool = False,
+                  correction: Optional[torch.Tensor] = None, group_top: int = 1, normalize: bool = False):
+    """Scores = softmax of the float32 `logits` over all experts (or, with `sigmoid`, the sigmoid of each); of
+    `groups` equal groups of neighbouring experts the `keep` with the largest best score (or sum of the two best, with
+    `group_top` 2) stay; (the `top` experts with the largest scores among those int32 [n, top] in falling order, their
+    scores times `scale` float32).  `correction` float32 [experts] is added to the scores that choose groups and
+    experts, not to the weights; `normalize` divides the weights by their sum (+ 1e-20) before the factor."""
     l = require_gpu()
     _rows(logits, "logits", torch.float32)
     n, E = logits.shape
     idx = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     wt = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    if correction is not None:
+        _dense(correction, "correction", torch.float32)
+        if correction.numel() != E:
+            raise KernelError(f"a correction of {correction.numel()} elements for {E} experts")
     check(l.gi_router_select(_ptr(logits), logits.stride(0), E, int(top), int(groups), int(keep), float(scale), _ptr(idx),
-                             _ptr(wt), n, _stream()), l)
+                             _ptr(wt), n, int(sigmoid), _ptr(correction), int(group_top), int(normalize), _stream()), l)
     return idx, wt
 
 
 def moe_rowwise(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor,
-                activation) -> torch.Tensor:
-    """sum_j wt[t, j] W_down[idx[t, j]] act(W_up[idx[t, j]] x[t]) with the chosen experts read from device memory:
+                activation, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """(add[t] +) sum_j wt[t, j] W_down[idx[t, j]] act(W_up[idx[t, j]] x[t]) with the chosen experts read from device memory:
     w_up [E, ff, hidden] and `activation` "relu_squared" or "silu", or w_up [E, 2 ff, hidden] (gate rows, then up
     rows) and a `glu_shape` tuple; w_down [E, hidden, ff]; one row of x at a time (decode steps)."""
     l = require_gpu()
@@ -485,7 +544,7 @@ def moe_rowwise(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, idx: 
     check(l.gi_moe_up(_ptr(x), x.stride(0), _ptr(w_up), _ptr(idx), _ptr(a), code(x.dtype), n, top, E, ff, hidden, act,
                       *unit, _stream()), l)
     check(l.gi_moe_down(_ptr(a), _ptr(w_down), _ptr(idx), _ptr(part), code(x.dtype), n, top, E, ff, hidden, _stream()), l)
-    return moe_combine(part, None, wt)
+    return moe_combine(part, None, wt, add)
 
 
 def moe_group(idx: torch.Tensor, x: torch.Tensor, n_experts: int):
@@ -506,15 +565,22 @@ def moe_group(idx: torch.Tensor, x: torch.Tensor, n_experts: int):
     return where, ends, rows
 
 
-def moe_combine(buf: torch.Tensor, where: Optional[torch.Tensor], wt: torch.Tensor) -> torch.Tensor:
-    """y[t] = sum_j wt[t, j] buf[where[t, j]] (float32 sums in the order of j); without `where`: row t * top + j."""
+def moe_combine(buf: torch.Tensor, where: Optional[torch.Tensor], wt: torch.Tensor,
+                add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[t] = (add[t] +) sum_j wt[t, j] buf[where[t, j]] (float32 sums in the order of j); without `where`: row
+    t * top + j."""
     l = require_gpu()
     _dense(buf, "buf"), _dense(wt, "wt", torch.float32)
     if where is not None:
         _dense(where, "where", torch.int32)
     n, top = wt.shape
+    if add is not None:
+        _dense(add, "add", buf.dtype)
+        if add.shape != (n, buf.shape[1]):
+            raise KernelError(f"an addend {tuple(add.shape)} for a result of {(n, buf.shape[1])}")
     y = torch.empty((n, buf.shape[1]), dtype=buf.dtype, device=buf.device)
-    check(l.gi_moe_combine(_ptr(buf), _ptr(where), _ptr(wt), _ptr(y), code(buf.dtype), n, top, buf.shape[1], _stream()), l)
+    check(l.gi_moe_combine(_ptr(buf), _ptr(where), _ptr(wt), _ptr(y), code(buf.dtype), n, top, buf.shape[1], _ptr(add),
+                           _stream()), l)
     return y
 
 
@@ -591,7 +657,8 @@ def scan_state_floats(key_dim: int, value_dim: int) -> int:
 
 
 def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, tok_slot: torch.Tensor,
-                     activation: str = "silu", renew_state: bool = False) -> torch.Tensor:
+                     activation: str = "silu", renew_state: bool = False, in_bias: Optional[torch.Tensor] = None,
+                     out_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """silu (or, with activation "none", the plain sum) of the causal convolution over time of x [n, C] (rows may lie apart) with taps [C, K], the K-1 inputs
     before the step's first token of a sequence taken from `state` [slots, >= (K-1) C] (a view of float32 state
     rows); returns float32 [n, C].  Call `conv_state_update` afterwards, or pass `renew_state` when no two rows of
@@ -600,20 +667,78 @@ def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, t
     _rows(x, "x"), _dense(taps, "taps"), _rows(state, "state", torch.float32), _dense(tok_slot, "tok_slot", torch.int32)
     n, C = x.shape
     out = torch.empty((n, C), dtype=torch.float32, device=x.device)
-    check(l.gi_causal_conv(_ptr(x), x.stride(0), code(x.dtype), C, _ptr(taps), code(taps.dtype), taps.shape[1],
-                           _ptr(state), state.stride(0), _ptr(tok_slot), _ptr(out), n, 2 if renew_state else 0,
-                           {"none": 0, "silu": 1}[activation], _stream()), l)
+    bias_dtype = _bias_pair(in_bias, out_bias, C)
+    check(l.gi_causal_conv_biased(_ptr(x), x.stride(0), code(x.dtype), C, _ptr(taps), code(taps.dtype), taps.shape[1],
+                                  _ptr(state), state.stride(0), _ptr(tok_slot), _ptr(out), n, 2 if renew_state else 0,
+                                  {"none": 0, "silu": 1}[activation], _ptr(in_bias), _ptr(out_bias), bias_dtype,
+                                  _stream()), l)
     return out
 
 
-def conv_state_update(x: torch.Tensor, n_taps: int, state: torch.Tensor, tok_slot: torch.Tensor) -> None:
-    """Each sequence's state becomes the last K-1 inputs it has seen (this step's rows, then what the state held)."""
+def _bias_pair(in_bias, out_bias, C: int) -> int:
+    """The one dtype code of a convolution's two optional biases [C]."""
+    given = [b for b in (in_bias, out_bias) if b is not None]
+    for b in given:
+        _dense(b, "bias")
+        if b.numel() != C or b.dtype != given[0].dtype:
+            raise KernelError(f"a bias of {b.numel()} {b.dtype} elements for {C} channels (both biases share a type)")
+    return code(given[0].dtype) if given else F32
+
+
+def conv_state_update(x: torch.Tensor, n_taps: int, state: torch.Tensor, tok_slot: torch.Tensor,
+                      in_bias: Optional[torch.Tensor] = None) -> None:
+    """Each sequence's state becomes the last K-1 inputs it has seen (this step's rows, then what the state held);
+    `in_bias` [C] is added to the step's rows as the convolution adds it."""
     l = require_gpu()
     _rows(x, "x"), _rows(state, "state", torch.float32), _dense(tok_slot, "tok_slot", torch.int32)
     if n_taps <= 1:
         return
-    check(l.gi_causal_conv_silu(_ptr(x), x.stride(0), code(x.dtype), x.shape[1], None, F32, n_taps, _ptr(state),
-                                state.stride(0), _ptr(tok_slot), None, x.shape[0], 1, _stream()), l)
+    check(l.gi_causal_conv_biased(_ptr(x), x.stride(0), code(x.dtype), x.shape[1], None, F32, n_taps, _ptr(state),
+                                  state.stride(0), _ptr(tok_slot), None, x.shape[0], 1, 1, _ptr(in_bias), None,
+                                  _bias_pair(in_bias, None, x.shape[1]), _stream()), l)
+
+
+def rglru_gates(u: torch.Tensor, wa_t: torch.Tensor, wi_t: torch.Tensor, ba: torch.Tensor, bi: torch.Tensor,
+                lam: torch.Tensor, decay_scale: float):
+    """The decay and the gated input of a real-gated linear recurrent unit from its input u float32 [n, width]:
+    per block of channels r = sigmoid(Wa u + ba), i = sigmoid(Wi u + bi) with the matrices given transposed
+    ([blocks, in, out]); a = exp(-decay_scale r softplus(lam)), b = sqrt(1 - a^2) i u.  Returns (a, b) float32."""
+    l = require_gpu()
+    _dense(u, "u", torch.float32), _dense(wa_t, "wa_t"), _dense(wi_t, "wi_t", wa_t.dtype)
+    n, width = u.shape
+    blocks, bw, bw2 = wa_t.shape
+    if bw != bw2 or blocks * bw != width or wi_t.shape != wa_t.shape:
+        raise KernelError(f"gate matrices {tuple(wa_t.shape)} / {tuple(wi_t.shape)} for {width} channels")
+    for v, name in ((ba, "ba"), (bi, "bi"), (lam, "lam")):
+        _dense(v, name, ba.dtype)
+        if v.numel() != width:
+            raise KernelError(f"{name} has {v.numel()} elements for {width} channels")
+    a = torch.empty((n, width), dtype=torch.float32, device=u.device)
+    b = torch.empty((n, width), dtype=torch.float32, device=u.device)
+    check(l.gi_rglru_gates(_ptr(u), _ptr(wa_t), _ptr(wi_t), code(wa_t.dtype), _ptr(ba), _ptr(bi), _ptr(lam), code(ba.dtype),
+                           float(decay_scale), _ptr(a), _ptr(b), n, width, blocks, _stream()), l)
+    return a, b
+
+
+def rglru_scan(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
+               spans: Optional[torch.Tensor], tok_slot: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """S <- a_t S + b_t along every sequence's rows from and into `state` (float32 rows per slot, the first `width`
+    columns); returns S_t * gelu_tanh(y_t + y_bias) in y's type.  y and `out` may be columns of wider matrices."""
+    l = require_gpu()
+    _dense(a, "a", torch.float32), _dense(b, "b", torch.float32), _rows(y, "y"), _rows(state, "state", torch.float32)
+    n, width = a.shape
+    if y.shape != (n, width) or b.shape != a.shape:
+        raise KernelError(f"a {tuple(a.shape)}, b {tuple(b.shape)} and y {tuple(y.shape)} differ")
+    if y_bias is not None:
+        _dense(y_bias, "y_bias")
+    if out is None:
+        out = torch.empty((n, width), dtype=y.dtype, device=y.device)
+    _rows(out, "out", y.dtype)
+    spans, n_seqs = _scan_args(spans, tok_slot, n)
+    check(l.gi_rglru_scan(_ptr(a), _ptr(b), _ptr(y), y.stride(0), code(y.dtype), _ptr(y_bias),
+                          code(y_bias.dtype) if y_bias is not None else F32, _ptr(state), state.stride(0), _ptr(spans),
+                          _ptr(tok_slot), _ptr(out), out.stride(0), n_seqs, width, _stream()), l)
+    return out
 
 
 def _scan_args(spans: Optional[torch.Tensor], tok_slot: torch.Tensor, n_rows: int):
@@ -1043,8 +1168,9 @@ def _masked_shapes(q, k_pool, v_pool, maps):
 
 def attention_prefill_masked_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                                   q_tiles: torch.Tensor, scale: float, window: int = 0, chunk: int = 0, maps: int = 1,
-                                  rows_covered: bool = False) -> torch.Tensor:
-    """The tensor-core prompt kernel with a chunk mask, values of a size of their own and `maps` softmax maps per
+                                  rows_covered: bool = False, sinks: Optional[torch.Tensor] = None,
+                                  dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The tensor-core prompt kernel with a chunk mask, optional `sinks` and `dist_bias` (as `attention_masked`), values of a size of their own and `maps` softmax maps per
     head over the same values: q [n, heads * maps, d] (a head's maps side by side), keys [pages, key/value heads *
     maps, page, d], values [pages, key/value heads, page, dv].  Returns [n, heads * maps * dv], a head's maps side
     by side."""
@@ -1054,17 +1180,19 @@ def attention_prefill_masked_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool:
     n, rows, d, dv, n_pages, n_kv, page_size = _masked_shapes(q, k_pool, v_pool, maps)
     if q_tiles.dim() != 2 or q_tiles.shape[1] != 4 or q_tiles.data_ptr() % 16:
         raise KernelError("q_tiles must be int32 [n_tiles, 4] starting on 16 bytes")
+    n_dist = _check_sinks_bias(sinks, dist_bias, rows)
     out = (torch.empty if rows_covered else torch.zeros)((n, rows * dv), dtype=q.dtype, device=q.device)
     check(l.gi_attention_prefill_masked_bf16(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(q_tiles),
                                              q_tiles.shape[0], _ptr(out), rows // maps, n_kv, d, dv, page_size,
                                              block_table.shape[1], n_pages, int(window or 0), int(chunk or 0), int(maps),
-                                             float(scale), _stream()), l)
+                                             float(scale), _ptr(sinks), _ptr(dist_bias), n_dist, _stream()), l)
     return out
 
 
 def attention_decode_masked_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                                  tok_pos: torch.Tensor, tok_slot: torch.Tensor, scale: float, window: int = 0,
-                                 chunk: int = 0, maps: int = 1, n_splits: Optional[int] = None) -> torch.Tensor:
+                                 chunk: int = 0, maps: int = 1, n_splits: Optional[int] = None,
+                                 sinks: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The split-KV decode kernel with the same options: one token per sequence, q [n_seqs, heads * maps, d].
     Returns [n_seqs, heads * maps * dv]."""
     l = require_gpu()
@@ -1074,13 +1202,15 @@ def attention_decode_masked_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     n, rows, d, dv, n_pages, n_kv, page_size = _masked_shapes(q, k_pool, v_pool, maps)
     heads = rows // maps
     n_splits = n_splits or decode_splits(n, n_kv * maps)
+    n_dist = _check_sinks_bias(sinks, dist_bias, rows)
     out = torch.empty((n, rows * dv), dtype=q.dtype, device=q.device)
     part_o = torch.empty((n * rows * n_splits * dv,), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((n * rows * n_splits * 2,), dtype=torch.float32, device=q.device)
     check(l.gi_attention_decode_masked_bf16(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(tok_pos),
                                             _ptr(tok_slot), _ptr(out), _ptr(part_o), _ptr(part_ml), n, heads, n_kv, d, dv,
                                             page_size, block_table.shape[1], n_pages, int(window or 0), int(chunk or 0),
-                                            int(maps), float(scale), n_splits, _stream()), l)
+                                            int(maps), float(scale), n_splits, _ptr(sinks), _ptr(dist_bias), n_dist,
+                                            _stream()), l)
     counters.launches += 1                                   # the combine kernel
     return out
 

@@ -25,15 +25,16 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 _SIGNATURES = {
     "gi_device_arch": ([], I),
     "gi_embedding": ([P, P, I, P, I, I, I, F, P], I),
-    "gi_add_rmsnorm": ([P, P, P, I, P, I, P, I, I, F, I, P], I),
+    "gi_add_rmsnorm": ([P, P, P, I, P, I, P, I, I, F, I, P, I, P], I),
+    "gi_residual_add_row": ([P, I, P, L, I, P], I),
     "gi_residual_add": ([P, I, P, L, P], I),
     "gi_swiglu": ([P, P, I, I, I, P], I),
     "gi_cast": ([P, I, P, I, L, P], I),
     "gi_qk_norm_rope_append": ([P, P, P, P, I, P, P, I, F, P, P, I, P, P, P,
                                 I, I, I, I, I, I, I, I, I, P, P], I),
     "gi_attention_generic": ([P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, I, P, P], I),
-    "gi_attention_masked": ([P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, I, P, I, I, I, I, P, P], I),
-    "gi_attn_prepare": ([P, I, L, I, I, I, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P], I),
+    "gi_attention_masked": ([P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, I, P, I, I, I, I, P, P, I, P], I),
+    "gi_attn_prepare": ([P, I, L, I, I, I, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, I, P, I, F, F, I, P], I),
     "gi_attn_finish": ([P, I, I, P, F, I, F, P, L, P, L, I, I, I, I, P], I),
     "gi_add_dyt": ([P, P, I, P, P, P, P, I, P, I, P, I, I, I, P], I),
     "gi_residual_add_scaled": ([P, I, P, I, P, I, I, P], I),
@@ -41,7 +42,7 @@ _SIGNATURES = {
     "gi_add_layernorm": ([P, P, P, P, P, I, P, I, P, I, I, F, I, P], I),
     "gi_rmsnorm_rows": ([P, L, P, I, P, I, I, I, F, P], I),
     "gi_softcap": ([P, L, F, P], I),
-    "gi_router_select": ([P, L, I, I, I, I, F, P, P, I, P], I),
+    "gi_router_select": ([P, L, I, I, I, I, F, P, P, I, I, P, I, I, P], I),
     "gi_relu_squared": ([P, P, I, L, P], I),
     "gi_scaled_sum": ([P, F, P, F, P, I, L, P], I),
     "gi_router_logits": ([P, L, I, P, P, I, I, I, P], I),
@@ -49,8 +50,11 @@ _SIGNATURES = {
     "gi_moe_up": ([P, L, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, P], I),
     "gi_moe_down": ([P, P, P, P, I, I, I, I, I, I, P], I),
     "gi_moe_group": ([P, P, L, I, P, P, P, P, I, I, I, I, P], I),
-    "gi_moe_combine": ([P, P, P, P, I, I, I, I, P], I),
+    "gi_moe_combine": ([P, P, P, P, I, I, I, I, P, P], I),
     "gi_causal_conv": ([P, L, I, I, P, I, I, P, L, P, P, I, I, I, P], I),
+    "gi_causal_conv_biased": ([P, L, I, I, P, I, I, P, L, P, P, I, I, I, P, P, I, P], I),
+    "gi_rglru_gates": ([P, P, P, I, P, P, P, I, F, P, P, I, I, I, P], I),
+    "gi_rglru_scan": ([P, P, P, L, I, P, I, P, L, P, P, P, L, I, I, P], I),
     "gi_gate_norm_add": ([P, L, P, L, P, I, P, I, P, P, I, I, I, F, P], I),
     "gi_xielu": ([P, L, P, I, P, I, I, I, P], I),
     "gi_gated_group_rmsnorm": ([P, P, L, P, I, I, P, I, I, I, I, F, I, F, L, P], I),
@@ -62,8 +66,8 @@ _SIGNATURES = {
     "gi_latent_decode": ([P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P], I),
     "gi_latent_prepare": ([P, L, I, P, L, I, I, P, I, P, I, F, P, F, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P], I),
     "gi_attention_prefill_bf16": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, P], I),
-    "gi_attention_prefill_masked_bf16": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, I, F, P], I),
-    "gi_attention_decode_masked_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P], I),
+    "gi_attention_prefill_masked_bf16": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, I, F, P, P, I, P], I),
+    "gi_attention_decode_masked_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P, I, P], I),
     "gi_attention_mma_takes": ([I, I], I),
     "gi_attention_prefill_tcgen05": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, P, P], I),
     "gi_attention_decode_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P], I),

@@ -1,9 +1,9 @@
 """Parts a model is put together from; importing this package registers the built-in ones."""
 from .base import (Block, Embedding, FeedForward, Gate, Head, Mixer, Norm, Part, PositionEncoding, Runtime,
-                   StepContext, StepShape, known_parts, part_class, register_part)
+                   StepContext, StepShape, StreamOffset, known_parts, part_class, register_part)
 from .attention import GQAAttention
 from .block import (ChannelScale, LinearHead, ParallelResidualBlock, PostNormGatedResidualBlock, PreNormResidualBlock,
-                    PreNormScaledResidualBlock, SigmoidGate, TokenEmbedding)
+                    PreNormScaledResidualBlock, SigmoidGate, StreamOffsetTable, TokenEmbedding)
 from .delta_rule import GatedDeltaRule
 from .latent_attention import LatentAttention
 from .linear_attention import DecayLinearAttention
@@ -12,6 +12,7 @@ from .mlp import GluMLP, SwiGLUMLP, XieluMLP
 from .moe import RoutedExperts
 from .norm import DynamicTanhNorm, LayerNorm, RMSNorm
 from .parallel import ParallelMixers
+from .rglru import RGLRU
 from .rotary import RotaryPositions
 
 __all__ = ["Block", "Embedding", "FeedForward", "Gate", "Head", "PostNormGatedResidualBlock", "SigmoidGate",
@@ -19,4 +20,5 @@ __all__ = ["Block", "Embedding", "FeedForward", "Gate", "Head", "PostNormGatedRe
            "Runtime", "StepContext", "StepShape", "known_parts", "part_class", "register_part", "GQAAttention",
            "LinearHead", "PreNormResidualBlock", "TokenEmbedding", "SwiGLUMLP", "RMSNorm", "RotaryPositions",
            "ChannelScale", "PreNormScaledResidualBlock", "MaskedAttention", "GluMLP", "RoutedExperts",
-           "DynamicTanhNorm", "ParallelMixers", "ParallelResidualBlock", "LayerNorm"]
+           "DynamicTanhNorm", "ParallelMixers", "ParallelResidualBlock", "LayerNorm", "RGLRU", "StreamOffset",
+           "StreamOffsetTable"]

@@ -16,6 +16,7 @@ register the class and name its kind in a plan.
     class Block(Part)            step(delta, residual, ctx, cache, writes_cache) -> delta
     class Gate(Part)             logits(x) -> [n, hidden]; the arrangement applies sigmoid(logits + bias)
     class Embedding(Part)        step(ctx) -> residual (float32)
+    class StreamOffset(Part)     row(i) -> a learned vector [hidden] that joins the stream where the schedule says
     class Head(Part)             step(normed_rows) -> logits (float32)
 
 What a part may read of the batch.  Always, on the device: `ctx.tok_pos` and `ctx.tok_slot` (the
@@ -112,6 +113,9 @@ class StepContext:
     # A second pending result in the activation type that joins the stream together with the pending delta (blocks
     # whose mixer and feed-forward read one normed input); the next norm adds both in float32.  None: nothing.
     delta_extra: Optional[torch.Tensor] = None
+    # A vector [hidden] that joins every row of the stream before the next block reads it (set by the model for
+    # a scheduled run that has one); a block hands it to its first norm or adds it itself, and clears it.
+    stream_offset: Optional[torch.Tensor] = None
 
     def seq_spans(self) -> Optional[torch.Tensor]:
         """int32 [n_seq, 3] = {slot, first row, rows} on the device for kernels that walk each sequence's rows
@@ -175,6 +179,9 @@ class FeedForward(Part):
 
 
 class Norm(Part):
+    # True for norms whose `add_norm` takes `offset`, a vector [size] that joins every row with the pending delta
+    takes_offset = False
+
     def add_norm(self, delta, residual, rows=None, write_residual=True, delta_scale=None, delta2=None):
         """normed(residual + delta * delta_scale + delta2); `delta_scale` (a factor per channel) is only passed by
         arrangements that scale their sublayers' results and `delta2` (a second pending result) only by arrangements
@@ -215,4 +222,9 @@ class Embedding(Part):
 
 class Head(Part):
     def step(self, normed):
+        raise NotImplementedError
+
+
+class StreamOffset(Part):
+    def row(self, i: int):
         raise NotImplementedError

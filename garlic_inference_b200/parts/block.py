@@ -4,6 +4,10 @@
     r = h;  x = norm_in(h);  r = mixer(x) + r;  x = norm_post(r);  h = ffn(x) + r
 The residual stream is float32; each add happens inside the norm that
 follows it, so the block takes and returns a pending `delta` (see base.py).
+The feed-forward may be absent (then the mixer's result is returned pending).
+A vector that the schedule adds to the stream before the layer
+(`ctx.stream_offset`, a row of a `stream_offset` table) rides in the first
+norm's kernel; the other arrangements add it with a kernel of its own.
 
 `post_norm_gated_residual` (no upstream counterpart): the sublayers read the
 stream itself and the norm sits on each sublayer's result, behind a gate that
@@ -33,7 +37,7 @@ import torch
 
 from ..ops import kernels, linear
 from ..weights.loader import TensorWant
-from .base import Block, Embedding, Gate, Head, register_part
+from .base import Block, Embedding, Gate, Head, StreamOffset, register_part
 
 
 def settle_scaled(delta, residual, ctx):
@@ -45,6 +49,14 @@ def settle_scaled(delta, residual, ctx):
     ctx.delta_scale = None
     settle_extra(residual, ctx)
     return delta
+
+
+def settle_offset(residual, ctx):
+    """A vector that joins every row of the stream before this block (set by the model from the schedule) is added
+    now, by arrangements whose first norm does not take it along."""
+    if ctx.stream_offset is not None:
+        kernels.residual_add_row(ctx.stream_offset, residual)
+        ctx.stream_offset = None
 
 
 def settle_extra(residual, ctx):
@@ -61,27 +73,35 @@ class PreNormResidualBlock(Block):
     def __init__(self, mixer, feed_forward, norms, position, rt):
         self.rt = rt
         self.mixer, self.feed_forward, self.position = mixer, feed_forward, position
-        missing = [n for n in self.norm_names if n not in norms]
+        need = self.norm_names if feed_forward is not None else self.norm_names[:1]
+        missing = [n for n in need if n not in norms]
         if missing:
-            raise ValueError(f"block 'pre_norm_residual' needs norms {self.norm_names}; missing {missing}")
-        self.norm_in, self.norm_post = norms["input"], norms["post_mixer"]
+            raise ValueError(f"block 'pre_norm_residual' needs norms {need}; missing {missing}")
+        self.norm_in, self.norm_post = norms["input"], norms.get("post_mixer")
 
     def cache_requirement(self):
         return self.mixer.cache_requirement()
 
     @property
     def graph_safe(self):
-        return all(p.graph_safe for p in (self.mixer, self.feed_forward, self.norm_in, self.norm_post)) and \
-            (self.position is None or self.position.graph_safe)
+        parts = (self.mixer, self.feed_forward, self.norm_in, self.norm_post, self.position)
+        return all(p.graph_safe for p in parts if p is not None)
 
     def step_arrays(self, shape, cache):
-        return {**self.mixer.step_arrays(shape, cache), **self.feed_forward.step_arrays(shape, cache)}
+        ff = self.feed_forward.step_arrays(shape, cache) if self.feed_forward is not None else {}
+        return {**self.mixer.step_arrays(shape, cache), **ff}
 
     def step(self, delta, residual, ctx, cache, writes_cache=True):
         ctx.residual_act = None                     # this block changes the stream and keeps no rounded copy
         delta = settle_scaled(delta, residual, ctx)
-        x = self.norm_in.add_norm(delta, residual)
+        offset = {}
+        if ctx.stream_offset is not None and self.norm_in.takes_offset:
+            offset, ctx.stream_offset = {"offset": ctx.stream_offset}, None
+        settle_offset(residual, ctx)
+        x = self.norm_in.add_norm(delta, residual, **offset)
         a = self.mixer.step(x, ctx, cache, self.position, writes_cache)
+        if self.feed_forward is None:
+            return a
         x = self.norm_post.add_norm(a, residual)
         return self.feed_forward.step(x, ctx)
 
@@ -141,6 +161,9 @@ class PostNormGatedResidualBlock(Block):
     def step(self, delta, residual, ctx, cache, writes_cache=True):
         act = self.rt.dtype
         delta = settle_scaled(delta, residual, ctx)
+        if ctx.stream_offset is not None:
+            ctx.residual_act = None
+        settle_offset(residual, ctx)
         if delta is not None:                       # a block before this one left its result pending
             kernels.residual_add(delta, residual)
             ctx.residual_act = None
@@ -204,6 +227,7 @@ class PreNormScaledResidualBlock(Block):
     def step(self, delta, residual, ctx, cache, writes_cache=True):
         ctx.residual_act = None
         settle_extra(residual, ctx)
+        settle_offset(residual, ctx)
         scale = lambda g: g.weight if g is not None else None
         x = self.norm_in.add_norm(delta, residual, delta_scale=ctx.delta_scale if delta is not None else None)
         y = self.mixer.step(x, ctx, cache, self.position, writes_cache)
@@ -251,6 +275,7 @@ class ParallelResidualBlock(Block):
             kernels.residual_add_scaled(delta, ctx.delta_scale, residual)
             delta = None
         ctx.delta_scale = None
+        settle_offset(residual, ctx)
         extra, ctx.delta_extra = ctx.delta_extra, None
         x = self.norm_in.add_norm(delta, residual, **({"delta2": extra} if extra is not None else {}))
         if self.w_out is not None:
@@ -304,6 +329,27 @@ class LinearHead(Head):
         return kernels.softcap_(logits, self.softcap) if self.softcap else logits
 
 
+class StreamOffsetTable(StreamOffset):
+    """A table of learned vectors [rows, hidden]; the schedule names the row that joins every token's residual stream
+    before a layer run (a vector per pass of layers that run several times, for instance).  Upstream has none."""
+    kind = "stream_offset"
+    graph_safe = True
+
+    @classmethod
+    def wanted(cls, params):
+        return {"weight": TensorWant((params["rows"], params["hidden_size"]))}
+
+    def __init__(self, params, load, rt):
+        super().__init__(params, load, rt)
+        table = load("weight")
+        # a tensor per row, so that each starts on an allocation's boundary (the norm kernel reads 16 bytes at a time)
+        self.rows = [table[i].clone().contiguous() for i in range(table.shape[0])]
+
+    def row(self, i: int):
+        return self.rows[i]
+
+
+register_part(StreamOffsetTable.kind, StreamOffsetTable)
 register_part(PreNormResidualBlock.kind, PreNormResidualBlock)
 register_part(PostNormGatedResidualBlock.kind, PostNormGatedResidualBlock)
 register_part(PreNormScaledResidualBlock.kind, PreNormScaledResidualBlock)

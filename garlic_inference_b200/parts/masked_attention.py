@@ -12,7 +12,18 @@
                       o = a_1 - lam a_2,  lam = exp(lq1 . lk1) - exp(lq2 . lk2) + diff     (one number per layer)
     sub_norm_eps:     o <- o / sqrt(mean(o^2) + eps) per head (no weight), times `out_mul`
     head_gate:        o <- o * sigmoid(Wg x)_head, one number per head, from the mixer's own input
+    qkv_bias:         q, k, v <- q + bq, k + bk, v + bv (tensors `q.b`, `k.b`, `v.b`), before everything else
+    projection_norm_eps:  q <- q / sqrt(mean(q^2) + eps) * wq over ALL query columns of the token at once (not per
+                      head), k likewise with wk (tensors `q.norm`, `k.norm`, a weight per column, used as they are)
+    query_temperature {coef, every}:  q at position p times 1 + coef ln(floor((p + 1) / every) + 1)
+    sink s:           the softmax's denominator also holds exp(s): a key that every query sees and that has no
+                      value (s = 0 adds one to the denominator)
+    distance_bias {rows B, max_distance D}:  the scaled score of key j for the query at position i gets
+                      rel[bucket(i - j), head] added (tensor `rel` [B, heads]; the scale does not touch it), with
+                      bucket(n) = n for n < B/2, else min(B - 1, B/2 + floor(ln(n / (B/2)) / ln(D / (B/2)) (B - B/2)))
     y = Wo concat(o)
+Bias, norm, temperature and rotation are float32 inside the kernel that also appends keys and values to the cache;
+sinks and distance biases (one map per head only) are taken by all three attention kernels below.
 
 Query head h reads key/value head h // (n_heads // n_kv_heads).  With `own_kv` False the layer has no key and
 value tensors: the schedule points it at another layer's cache entry, whose keys and values (as that cache holds
@@ -28,6 +39,8 @@ comes out is combined, normed and gated in float32 and rounded once.  Upstream h
 (src/models/qwen3/qwen3.cpp:140-179).
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -66,7 +79,28 @@ class MaskedAttention(Mixer):
                 w[n] = TensorWant((d,), std_scale=5.0)
         if params.get("head_gate", False):
             w["g"] = TensorWant((H, hid))
+        if params.get("qkv_bias", False):
+            w["q.b"] = TensorWant((H * maps * d,))
+            if own:
+                w["k.b"], w["v.b"] = TensorWant((G * maps * d,)), TensorWant((G * dv,))
+        if params.get("projection_norm_eps") is not None:
+            w["q.norm"] = TensorWant((H * maps * d,), "norm")
+            if own:
+                w["k.norm"] = TensorWant((G * maps * d,), "norm")
+        if params.get("distance_bias"):
+            w["rel"] = TensorWant((int(params["distance_bias"]["rows"]), H))
         return w
+
+    @staticmethod
+    def distance_buckets(rows: int, max_distance: int) -> torch.Tensor:
+        """bucket(n) for n = 0 .. max_distance (every larger distance reads the last row, as max_distance itself
+        does): int64 [max_distance + 1].  The logarithms are float64."""
+        half = rows // 2
+        n = torch.arange(max_distance + 1, dtype=torch.float64)
+        if half == 0:
+            return torch.zeros(max_distance + 1, dtype=torch.long)
+        far = half + torch.floor(torch.log(torch.clamp(n, min=1.0) / half) / math.log(max_distance / half) * (rows - half))
+        return torch.where(n < half, n, torch.clamp(far, max=rows - 1)).to(torch.long)
 
     def __init__(self, params, load, rt):
         super().__init__(params, load, rt)
@@ -104,6 +138,33 @@ class MaskedAttention(Mixer):
                         + float(params.get("diff", 0.0))).reshape(1).contiguous()
         self.state_floats = -(-((self.K - 1) * self.C) // 4) * 4 if self.K > 1 else 0
         self._no_state = None
+        f32 = lambda t: t.to(torch.float32)
+        own_names = lambda stem: [stem.format("q")] + ([stem.format("k")] if self.own_kv else [])
+        self.bias = None
+        if params.get("qkv_bias", False):
+            self.bias = torch.cat([f32(load(n)) for n in own_names("{}.b") + (["v.b"] if self.own_kv else [])]).contiguous()
+        self.norm_eps = params.get("projection_norm_eps")
+        self.norm_w = None
+        if self.norm_eps is not None:
+            self.norm_w = torch.cat([f32(load(n)) for n in own_names("{}.norm")]).contiguous()
+        temp = params.get("query_temperature") or {}
+        self.temp_coef, self.temp_every = float(temp.get("coef", 0.0)), int(temp.get("every", 0))
+        if temp and self.temp_every <= 0:
+            raise ValueError(f"query_temperature.every must be positive, found {self.temp_every}")
+        self.sinks = None
+        if params.get("sink") is not None:
+            self.sinks = torch.full((self.H,), float(params["sink"]), dtype=torch.float32, device=rt.device)
+        self.dist_bias = None
+        if params.get("distance_bias"):
+            rows, far = int(params["distance_bias"]["rows"]), int(params["distance_bias"]["max_distance"])
+            if rows < 1 or far <= rows // 2:
+                raise ValueError(f"a distance bias of {rows} rows up to distance {far}: the distance must pass half the rows")
+            # the table by distance, [max_distance + 1, heads] float32: what the kernels index with min(i - j, last)
+            self.dist_bias = f32(load("rel"))[self.distance_buckets(rows, far).to(rt.device)].contiguous()
+        if (self.sinks is not None or self.dist_bias is not None) and self.maps != 1:
+            raise ValueError("a sink and a distance bias come with one softmax map per head")
+        if (self.bias is not None or self.norm_w is not None or self.temp_every) and self.K:
+            raise ValueError("biases, the projection norm and the query temperature are not combined with the short filters")
 
     def cache_requirement(self):
         kv = KVRequirement(self.G * self.maps, self.d, None, 2, value_heads=self.G, value_dim=self.dv)
@@ -117,7 +178,8 @@ class MaskedAttention(Mixer):
     def _run_rows(self, kv) -> int:
         """Height of the query runs of the prompt kernel that takes this mixer: 128 (tcgen05: one map, keys and
         values of 128, pages of a multiple of 64), 64 (mma.sync), 0 (the exact-order kernel, which needs none)."""
-        if self.maps == 1 and self.d == self.dv and kernels.tcgen05_attention_takes(self.rt.dtype, self.d, kv.page_size):
+        if self.maps == 1 and self.d == self.dv and self.sinks is None and self.dist_bias is None and \
+                kernels.tcgen05_attention_takes(self.rt.dtype, self.d, kv.page_size):
             return 128
         return 64 if self._tensor_cores() else 0
 
@@ -162,10 +224,14 @@ class MaskedAttention(Mixer):
         freq, n_rot, half = self._rotation(position)
         q = kernels.attn_prepare(src, 0, self.Cq if self.own_kv else -1, self.Cq + self.Ck, freq, n_rot, half,
                                  ctx.tok_pos, ctx.tok_slot, kv.block_table, kv.k_pool, kv.v_pool, self.H * self.maps,
-                                 self.d, self.rt.dtype, ctx.status, append=writes_cache)
+                                 self.d, self.rt.dtype, ctx.status, append=writes_cache, bias=self.bias,
+                                 norm_weight=self.norm_w, norm_eps=float(self.norm_eps or 0.0), temp_coef=self.temp_coef,
+                                 temp_every=self.temp_every)
+        extras = dict(sinks=self.sinks, dist_bias=self.dist_bias)
         if ctx.all_single and self._tensor_cores() and self.H // self.G <= 16:
             att = kernels.attention_decode_masked_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
-                                                       self.scale, window=self.window, chunk=self.chunk, maps=self.maps)
+                                                       self.scale, window=self.window, chunk=self.chunk, maps=self.maps,
+                                                       **extras)
         elif not ctx.all_single and ctx.seq_lens and self._run_rows(kv):
             rows = self._run_rows(kv)
             runs = ctx.arrays.get(f"query_runs_{rows}")
@@ -178,12 +244,15 @@ class MaskedAttention(Mixer):
             else:
                 att = kernels.attention_prefill_masked_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, runs, self.scale,
                                                             window=self.window, chunk=self.chunk, maps=self.maps,
-                                                            rows_covered=covered)
+                                                            rows_covered=covered, **extras)
         else:
             att = kernels.attention_masked(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
                                            self.scale, ctx.status, window=self.window, chunk=self.chunk,
-                                           maps=self.maps, out_float32=True)
+                                           maps=self.maps, out_float32=True, **extras)
         gate = proj[:, self.g_off:self.g_off + self.H] if self.head_gate else None
+        if self.maps == 1 and gate is None and self.sub_norm_eps is None and self.out_mul * out_mul == 1.0 and \
+                out is None and att.dtype == self.rt.dtype:
+            return att                                # one map, nothing to combine, norm or gate: it is the result
         return kernels.attn_finish(att, self.H, self.maps, self.lam, self.sub_norm_eps, self.out_mul * out_mul, gate,
                                    self.rt.dtype, out=out)
 

@@ -8,6 +8,14 @@
                                neighbours, a group's score is its largest s, and only the `groups_kept` best groups
                                stay; the `top` largest s among them are chosen; weights s * `weight_scale`, not
                                renormalised
+    scores "sigmoid":          s = sigmoid(z), each expert by itself; groups as above.  With `correction` (a tensor
+                               of one number per expert) the groups and the experts are chosen by s + correction
+                               while the weights stay s; experts of a group that does not stay cannot be chosen
+                               whatever their scores
+    `group_score` "top2_sum":  a group's score is the sum of its two largest choosing scores ("best": the largest)
+    `normalize`:               the chosen weights are divided by their sum (+ 1e-20) before `weight_scale`
+    `shared` {size, ...unit}:  one more gated expert (tensors `shared.gate`, `shared.up`, `shared.down`; its own
+                               limits) that every token runs and whose result is added with weight 1
     expert "two_matrix" (the default):  y = sum_e weight_e Wd_e act(Wu_e x), act the square of relu
                                ("relu_squared") or silu; no biases
     expert "glu":              y = sum_e weight_e Wd_e unit(Wg_e x, Wu_e x), a gated unit with `activation`,
@@ -29,7 +37,7 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import kernels, linear
+from ..ops import glu_product, kernels, linear
 from ..weights.loader import TensorWant
 from .base import FeedForward, register_part
 
@@ -47,7 +55,12 @@ class RoutedExperts(FeedForward):
     def wanted(cls, params):
         hid, ff, E = params["hidden_size"], params["expert_size"], params["n_experts"]
         # scores over all experts: random routers are made wider, so that random models choose with clear margins
-        w = {"router": TensorWant((E, hid), std_scale=4.0 if params.get("scores") == "softmax_all" else 1.0)}
+        w = {"router": TensorWant((E, hid), std_scale=4.0 if params.get("scores") in ("softmax_all", "sigmoid") else 1.0)}
+        if params.get("correction", False):
+            w["correction"] = TensorWant((E,), std_scale=5.0)
+        if params.get("shared"):
+            sf = int(params["shared"]["size"])
+            w["shared.gate"], w["shared.up"], w["shared.down"] = TensorWant((sf, hid)), TensorWant((sf, hid)), TensorWant((hid, sf))
         for e in range(E):
             if params.get("expert", "two_matrix") == "glu":
                 w[f"e{e}.gate"] = TensorWant((ff, hid))
@@ -73,18 +86,35 @@ class RoutedExperts(FeedForward):
         else:
             self.act = self.activation
         self.scores = params.get("scores", "softmax_chosen")
-        if self.scores not in ("softmax_chosen", "softmax_all"):
-            raise ValueError(f"router scores {self.scores!r} are neither 'softmax_chosen' nor 'softmax_all'")
+        if self.scores not in ("softmax_chosen", "softmax_all", "sigmoid"):
+            raise ValueError(f"router scores {self.scores!r} are none of 'softmax_chosen', 'softmax_all', 'sigmoid'")
+        self.group_score = params.get("group_score", "best")
+        if self.group_score not in ("best", "top2_sum"):
+            raise ValueError(f"group_score {self.group_score!r} is neither 'best' nor 'top2_sum'")
+        self.normalize = bool(params.get("normalize", False))
         self.groups, self.groups_kept = int(params.get("groups", 1)), int(params.get("groups_kept", params.get("groups", 1)))
         self.weight_scale = float(params.get("weight_scale", 1.0))
-        if self.scores == "softmax_all":
+        if self.scores in ("softmax_all", "sigmoid"):
             per = self.E // max(self.groups, 1)
             if self.groups <= 0 or self.E % self.groups or not 0 < self.groups_kept <= self.groups or \
                     self.top > self.groups_kept * per:
                 raise ValueError(f"{self.E} experts in {self.groups} groups of which {self.groups_kept} stay, top {self.top}")
-        elif self.groups != 1 or self.weight_scale != 1.0:
-            raise ValueError("groups of experts and a factor on the weights come with scores 'softmax_all'")
+        elif self.groups != 1 or self.weight_scale != 1.0 or self.normalize or params.get("correction", False):
+            raise ValueError("groups of experts, a correction and a factor on the weights come with scores over all experts")
         self.w_router = load("router").to(torch.float32)
+        self.correction = load("correction").to(torch.float32).contiguous() if params.get("correction", False) else None
+        self.shared = None
+        if params.get("shared"):
+            if not self.gated:
+                raise ValueError("a shared expert comes with gated experts")
+            sh = params["shared"]
+            sf = int(sh["size"])
+            self.shared_unit = kernels.glu_shape(sh.get("activation", self.activation), sh.get("swish_alpha", 1.0),
+                                                 sh.get("gate_max"), sh.get("up_limit"), sh.get("up_shift", 0.0))
+            self.shared = torch.empty((2 * sf, self.hidden), dtype=load.dtype("shared.gate", "shared.up"), device=rt.device)
+            load("shared.gate", out=self.shared[:sf])
+            load("shared.up", out=self.shared[sf:])
+            self.shared_down = load("shared.down")
         rows = 2 * self.ff if self.gated else self.ff
         names = [f"e{e}.{n}" for e in range(self.E) for n in (("gate", "up", "down") if self.gated else ("up", "down"))]
         dtype = load.dtype(*names)
@@ -99,8 +129,10 @@ class RoutedExperts(FeedForward):
     def route(self, x):
         """(chosen experts int32 [n, top], their weights float32 [n, top]) for the rows of x."""
         logits = kernels.router_logits(x, self.w_router)
-        if self.scores == "softmax_all":
-            return kernels.router_select(logits, self.top, self.groups, self.groups_kept, self.weight_scale)
+        if self.scores != "softmax_chosen":
+            return kernels.router_select(logits, self.top, self.groups, self.groups_kept, self.weight_scale,
+                                         sigmoid=self.scores == "sigmoid", correction=self.correction,
+                                         group_top=2 if self.group_score == "top2_sum" else 1, normalize=self.normalize)
         return kernels.router_topk(logits, self.top)
 
     def _activate(self, z):
@@ -109,10 +141,12 @@ class RoutedExperts(FeedForward):
     def step(self, x, ctx):
         n = x.shape[0]
         idx, wt = self.route(x)
+        # the shared expert's result joins the weighted sum inside the kernel that makes it, in float32
+        add = linear(glu_product(x, self.shared, self.shared_unit), self.shared_down) if self.shared is not None else None
         grouped = self._grouped(x)
         products = self.gated or self.activation == "relu_squared"     # what the expert-by-expert path computes
         if n <= ROWWISE_MAX_ROWS or not products or (ctx.captured and not grouped):
-            return kernels.moe_rowwise(x, self.w_up, self.w_down, idx, wt, self.act)
+            return kernels.moe_rowwise(x, self.w_up, self.w_down, idx, wt, self.act, add=add)
         # expert by expert: the pairs (token, choice) in the order of their experts; `where` is each pair's row
         where, ends, rows = kernels.moe_group(idx, x, self.E)
         if grouped:
@@ -128,7 +162,7 @@ class RoutedExperts(FeedForward):
                     a = self._activate(linear(rows[at:at + c], self.w_up[e]))
                     buf[at:at + c] = linear(a, self.w_down[e])
                     at += c
-        return kernels.moe_combine(buf.contiguous(), where, wt)
+        return kernels.moe_combine(buf.contiguous(), where, wt, add)
 
     def _grouped(self, x) -> bool:
         """Whether the library's grouped product takes these operands: bfloat16, rows of 16-byte multiples."""

@@ -25,6 +25,7 @@ from .base import Norm, register_part
 class RMSNorm(Norm):
     kind = "rms_norm"
     graph_safe = True
+    takes_offset = True
 
     @classmethod
     def wanted(cls, params):
@@ -36,17 +37,18 @@ class RMSNorm(Norm):
         self.eps = float(params["eps"])
         self.weight = load("weight")
 
-    def add_norm(self, delta, residual, rows=None, write_residual=True, delta_scale=None, delta2=None):
-        """normed(residual + delta) in the activation type.  The float32 sum is written back to
+    def add_norm(self, delta, residual, rows=None, write_residual=True, delta_scale=None, delta2=None, offset=None):
+        """normed(residual + delta (+ offset)) in the activation type.  The float32 sum is written back to
         `residual` unless `rows` picks rows or `write_residual` is False; `delta` may be None.  A scaled delta
-        is added to the stream by a kernel of its own first (then the stream is written whatever was asked)."""
+        is added to the stream by a kernel of its own first (then the stream is written whatever was asked).
+        `offset` [size] joins every row in the same kernel."""
         if delta2 is not None:
             kernels.residual_add(delta2, residual)
         if delta is not None and delta_scale is not None:
             kernels.residual_add_scaled(delta, delta_scale, residual)
             delta = None
         return kernels.add_rmsnorm(delta, residual, self.weight, self.eps, self.rt.dtype, rows=rows,
-                                   write_residual=write_residual)
+                                   write_residual=write_residual, offset=offset)
 
 
 class DynamicTanhNorm(Norm):
