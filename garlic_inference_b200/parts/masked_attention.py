@@ -80,15 +80,15 @@ class MaskedAttention(Mixer):
         if params.get("head_gate", False):
             w["g"] = TensorWant((H, hid))
         if params.get("qkv_bias", False):
-            w["q.b"] = TensorWant((H * maps * d,))
+            w["q.b"] = TensorWant((H * maps * d,), std_scale=5.0)
             if own:
-                w["k.b"], w["v.b"] = TensorWant((G * maps * d,)), TensorWant((G * dv,))
+                w["k.b"], w["v.b"] = TensorWant((G * maps * d,), std_scale=5.0), TensorWant((G * dv,), std_scale=5.0)
         if params.get("projection_norm_eps") is not None:
             w["q.norm"] = TensorWant((H * maps * d,), "norm")
             if own:
                 w["k.norm"] = TensorWant((G * maps * d,), "norm")
         if params.get("distance_bias"):
-            w["rel"] = TensorWant((int(params["distance_bias"]["rows"]), H))
+            w["rel"] = TensorWant((int(params["distance_bias"]["rows"]), H), std_scale=10.0)
         return w
 
     @staticmethod

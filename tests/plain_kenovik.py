@@ -12,9 +12,32 @@ in the dtype of `dtype` (float64 for the yardstick, float32 for its own rounding
 """
 from __future__ import annotations
 
+import json
 import math
+import struct
+from pathlib import Path
 
 import torch
+
+
+def read_safetensors(path) -> dict:
+    """{name: tensor} of a safetensors file: 8 bytes of length, that many of JSON, then the data."""
+    raw = Path(path).read_bytes()
+    n = struct.unpack("<Q", raw[:8])[0]
+    meta = json.loads(raw[8:8 + n])
+    types = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "I32": torch.int32}
+    out = {}
+    for name, m in meta.items():
+        if name == "__metadata__":
+            continue
+        a, b = m["data_offsets"]
+        out[name] = torch.frombuffer(bytearray(raw[8 + n + a:8 + n + b]), dtype=types[m["dtype"]]).reshape(m["shape"])
+    return out
+
+
+def read_model_dir(model_dir):
+    model_dir = Path(model_dir)
+    return json.loads((model_dir / "config.json").read_text()), read_safetensors(model_dir / "model.safetensors")
 
 
 def rms_norm(x, w, eps):
@@ -91,7 +114,8 @@ def attention_bias(h, W, m, positions, eps):
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = rms_norm(h @ W["q"].T, W["q.norm"], eps)
     k = rms_norm(h @ W["k"].T, W["k.norm"], eps)
-    q = q * query_temperature(positions, m["q_temp"]["coef"], m["q_temp"]["every"], h.dtype)[:, None]
+    if m.get("q_temp"):
+        q = q * query_temperature(positions, m["q_temp"]["coef"], m["q_temp"]["every"], h.dtype)[:, None]
     q, k = q.reshape(T, H, d), k.reshape(T, G, d)
     v = (h @ W["v"].T).reshape(T, G, dv)
     rel = W["rel"]                                                         # [rows, heads]
@@ -132,7 +156,7 @@ def rglru(h, W, m, state=None):
     i = torch.sigmoid(torch.einsum("tbi,boi->tbo", ub, W["ri"]) + W["ri.b"]).reshape(T, width)
     log_a = -8.0 * r * softplus(W["lam"])
     a = torch.exp(log_a)
-    b = torch.sqrt(1.0 - a * a) * i * u
+    b = torch.sqrt(torch.clamp(1.0 - a * a, min=0.0)) * i * u
     S = torch.zeros(width, dtype=h.dtype) if state is None else state
     out = torch.zeros(T, width, dtype=h.dtype)
     for t in range(T):
