@@ -1003,6 +1003,246 @@ def study_dugopel(args, pk) -> int:
     print(json.dumps(out))
     return 0
 
+# ---- the Kenovik design beside Qwen3 at equal layer sizes -------------------------------------------
+def kenovik_config_dict(width, heads, ff, vocab, passes, head_dim=128, experts=16, top=2, groups=4, keep=2):
+    """Three layers at sizes of a real model's (distance-bias attention + dense, recurrent block + experts, sink
+    attention + experts; experts of ff / top, so that a token's routed feed-forward has the dense one's parameters,
+    and a shared expert of half that) that run `passes` times in a row."""
+    kv = max(1, heads // 4)
+    att2 = {"heads": heads, "kv_heads": kv, "dim": head_dim, "vdim": head_dim // 2, "scale": head_dim ** -0.5,
+            "bias_max": 2048, "bias_rows": 64, "q_temp": {"coef": 0.1, "every": 512}}
+    att = {"heads": heads, "kv_heads": kv, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+           "rot": {"base": 1000000.0, "dims": head_dim // 2, "scaling": {"factor": 8.0}}}
+    rec = {"width": width * 5 // 4, "blocks": max(1, width // 256), "conv": 4}
+    eff = max(64, ff // top // 64 * 64)
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "shared": {"ff": eff // 2, "limit": 7.0},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups, "keep": keep}}}
+    layers = [{"type": "attention_2", "mixer": att2, "mlp": {"kind": "dense", "ff": ff}},
+              {"type": "rglru", "mixer": rec, "mlp": moe}, {"type": "attention", "mixer": att, "mlp": moe}]
+    return {"architecture": "Kenovik", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": layers, "loop": {"start": 0, "stop": 3, "times": passes}}
+
+
+def study_kenovik(args, pk) -> int:
+    """Prefill (one prompt of 2,048 tokens) and decode (batches of 1, 8 and 64 with 2,048 cached tokens each) of
+    Kenovik models with random weights, beside Qwen3 models of the same width, heads, feed-forward and number of layer
+    runs, and the design's kernels timed alone beside the closest kernels of the other models.  One JSON line."""
+    import torch
+    from garlic_inference_b200 import LanguageModel, Qwen3Config
+    from garlic_inference_b200.config import KenovikConfig
+    from garlic_inference_b200.ops import counters, kernels
+    from garlic_inference_b200.parts import Runtime, StepContext, StepShape, part_class
+    from garlic_inference_b200.parts.attention import query_runs
+    from garlic_inference_b200.sampling import SamplingParams
+    K, W = min(args.steps, 64), max(min(args.warmup, 8), 3)
+    torch.cuda.set_device(0)
+    greedy = SamplingParams()
+    gen = torch.Generator().manual_seed(0)
+    sizes = [("1b", 2048, 16, 8192, 32000, 3), ("8b", 4096, 32, 18432, 32000, 2)]
+    out = {"study": "kenovik", "dtype": "bfloat16", "data": "synthetic", "steps": K, "warmup": W,
+           "peaks": pk, "models": {}, "kernels": {}}
+
+    def timed(fn, reps=5, warm=3):
+        for _ in range(warm):
+            fn()
+        flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
+        ms = []
+        for _ in range(reps):
+            flush.zero_()                                  # larger than L2: the next run starts cold
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ms.append(a.elapsed_time(b))
+        return statistics.median(ms)
+
+    def run_model(cfg, vocab):
+        per_seq = -(-(CACHED + W + K + 8) // 64) * 64
+        model = LanguageModel.from_random(cfg, seed=0, device=0, dtype="bfloat16", max_tokens=64 * per_seq,
+                                          max_slots=64)
+        eng, sampler = model.engine, model.sampler
+        prompt = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+        res = {"weight_bytes": model.model.weight_bytes()}
+
+        def prefill_once():
+            s = eng.alloc_slot()
+            model.step([(s, prompt(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+            eng.free_slot(s)
+        ms = timed(prefill_once, reps=5, warm=3)
+        res["prefill"] = {"tokens": PREFILL_TOKENS, "ms": round(ms, 3), "tokens_per_s": round(PREFILL_TOKENS / ms * 1e3)}
+        for batch in (1, 8, 64):
+            slots, firsts = [], []
+            for _ in range(batch):
+                s = eng.alloc_slot()
+                firsts.append(sampler.sample(model.step([(s, prompt(CACHED), [CACHED - 1])]), greedy, [0], [0]))
+                slots.append(s)
+            toks = torch.cat(firsts)
+            for _ in range(W):
+                toks = sampler.sample(eng.step_decode_device(slots, toks), greedy, slots, slots)
+            torch.cuda.synchronize()
+            n0 = counters.launches
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(K):
+                toks = sampler.sample(eng.step_decode_device(slots, toks), greedy, slots, slots)
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / K
+            res[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3),
+                                       "launches_per_step": (counters.launches - n0) // K}
+            for s in slots:
+                eng.free_slot(s)
+        eng.check()
+        del model
+        torch.cuda.empty_cache()
+        return res
+
+    for label, width, heads, ff, vocab, passes in sizes:
+        kcfg = KenovikConfig.from_dict(kenovik_config_dict(width, heads, ff, vocab, passes))
+        qcfg = Qwen3Config(hidden_size=width, num_hidden_layers=3 * passes, num_attention_heads=heads,
+                           num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=ff,
+                           vocab_size=vocab, max_position_embeddings=CONTEXT * 2)
+        out["models"][label] = {"width": width, "heads": heads, "ff": ff, "layer_runs": 3 * passes,
+                                "kenovik": run_model(kcfg, vocab), "qwen3": run_model(qcfg, vocab)}
+
+    # ---- the kernels alone, at the larger size: 2,048 rows of a prompt, and 8 single tokens ----
+    width, H, G, d, T, page, ffd = 4096, 32, 8, 128, PREFILL_TOKENS, 64, 18432
+    dev = "cuda"
+    bf = lambda *shape: torch.randn(*shape, device=dev, dtype=torch.bfloat16) * 0.5
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    kern = out["kernels"]
+
+    def note(name, ms, flops=0.0, bytes_=0.0):
+        kern[name] = {"ms": round(ms, 4)}
+        if flops:
+            kern[name]["tflops"] = round(flops / ms / 1e9, 2)
+            kern[name]["of_measured_bf16"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 4)
+        if bytes_:
+            kern[name]["gbs"] = round(bytes_ / ms / 1e6, 1)
+            kern[name]["of_measured_copy"] = round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)
+
+    # the norm that takes a vector along, beside the plain one
+    w, off = bf(width), bf(width)
+    for n_rows in (T, 8):
+        res, d1 = torch.randn(n_rows, width, device=dev), bf(n_rows, width)
+        ms = timed(lambda: kernels.add_rmsnorm(d1, res, w, 1e-6, torch.bfloat16, offset=off))
+        note(f"add_offset_rmsnorm_{n_rows}", ms, bytes_=n_rows * width * (2 + 4 + 4 + 2))
+        ms = timed(lambda: kernels.add_rmsnorm(d1, res, w, 1e-6, torch.bfloat16))
+        note(f"add_rmsnorm_{n_rows}", ms, bytes_=n_rows * width * (2 + 4 + 4 + 2))
+    # attention: the flash kernel (mma.sync) with a sink, with a distance bias and bare; the tcgen05 kernel bare;
+    # the split-KV kernel for 8 single tokens likewise
+    table = torch.arange(8 * T // page, dtype=torch.int32, device=dev).view(8, T // page)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    sinks = torch.zeros(H, device=dev)
+    dist = torch.randn(2049, H, device=dev)
+    runs64 = torch.from_numpy(query_runs(StepShape([0], [0], [T], [0], False), 64)).to(dev)
+    runs128 = torch.from_numpy(query_runs(StepShape([0], [0], [T], [0], False), 128)).to(dev)
+    pos8, slots8 = i32([T - 1] * 8), i32(list(range(8)))
+    for dv, tag in ((128, "k128_v128"), (64, "k128_v64")):
+        kp, vp = bf(8 * T // page, G, page, d), bf(8 * T // page, G, page, dv)
+        qq, q8 = bf(T, H, d), bf(8, H, d)
+        fl = 2.0 * H * (d + dv) * T * (T + 1) / 2
+        by = 8 * T * G * (d + dv) * 2
+        for name, extra in (("bare", {}), ("sink", {"sinks": sinks}), ("distance_bias", {"dist_bias": dist})):
+            ms = timed(lambda: kernels.attention_prefill_masked_bf16(qq, kp, vp, table, runs64, 0.088, rows_covered=True, **extra))
+            note(f"attention_prefill2048_mma_{tag}_{name}", ms, flops=fl)
+            ms = timed(lambda: kernels.attention_decode_masked_bf16(q8, kp, vp, table, pos8, slots8, 0.088, **extra))
+            note(f"attention_decode_b8_mma_{tag}_{name}", ms, bytes_=by)
+        if dv == d:
+            ms = timed(lambda: kernels.attention_prefill_tcgen05(qq, kp, vp, table, runs128, 0.088, 0, rows_covered=True))
+            note(f"attention_prefill2048_tcgen05_{tag}_bare", ms, flops=fl)
+            ms = timed(lambda: kernels.attention_prefill_tcgen05(qq, kp, vp, table, runs128, 0.088, 0, rows_covered=True, sinks=sinks))
+            note(f"attention_prefill2048_tcgen05_{tag}_sink", ms, flops=fl)
+            ms = timed(lambda: kernels.attention_decode_tcgen05(q8, kp, vp, table, pos8, slots8, 0.088, 0))
+            note(f"attention_decode_b8_tcgen05_{tag}_bare", ms, bytes_=by)
+    # between projections and attention: biases + rotation of half of every head; projection norm + query factor;
+    # and Qwen3's kernel (per-head norms, rotation by table)
+    freq = torch.tensor([1e6 ** (-2.0 * i / 64) / 8.0 for i in range(32)], dtype=torch.float32, device=dev)
+    cols = (H + 2 * G) * d
+    bias, wn = torch.randn(cols, device=dev), torch.randn((H + G) * d, device=dev)
+    kp, vp = bf(8 * T // page, G, page, d), bf(8 * T // page, G, page, d)
+    for n_rows, pos, slot in ((T, torch.arange(T, dtype=torch.int32, device=dev), i32([0] * T)), (8, pos8, slots8)):
+        src = bf(n_rows, cols)
+        by = n_rows * cols * 2 * 2
+        ms = timed(lambda: kernels.attn_prepare(src, 0, H * d, (H + G) * d, freq, 64, False, pos, slot, table, kp, vp, H, d,
+                                                torch.bfloat16, status, bias=bias))
+        note(f"attn_prepare_bias_rotation_{n_rows}", ms, bytes_=by)
+        ms = timed(lambda: kernels.attn_prepare(src, 0, H * d, (H + G) * d, None, 0, False, pos, slot, table, kp, vp, H, d,
+                                                torch.bfloat16, status, norm_weight=wn, norm_eps=1e-6, temp_coef=0.1,
+                                                temp_every=512))
+        note(f"attn_prepare_projection_norm_{n_rows}", ms, bytes_=by)
+        ms = timed(lambda: kernels.attn_prepare(src, 0, H * d, (H + G) * d, None, 0, False, pos, slot, table, kp, vp, H, d,
+                                                torch.bfloat16, status))
+        note(f"attn_prepare_bare_{n_rows}", ms, bytes_=by)
+    # the recurrent block's kernels (5,120 channels in 16 blocks, 4 taps) beside the delta rule's scan (16 heads of 128 x 128)
+    Wd, B, Kt = 5120, 16, 4
+    bw = Wd // B
+    taps, xb, cb = bf(Wd, Kt), torch.randn(Wd, device=dev), torch.randn(Wd, device=dev)
+    wa, wi = bf(B, bw, bw) * 0.1, bf(B, bw, bw) * 0.1
+    ba, bi, lam = torch.randn(Wd, device=dev), torch.randn(Wd, device=dev), torch.randn(Wd, device=dev)
+    for n_rows, slot, spans in ((T, i32([0] * T), i32([[0, 0, T]])), (8, slots8, None)):
+        proj = bf(n_rows, 2 * Wd)
+        state = torch.zeros(9, Kt * Wd, device=dev)
+        ms = timed(lambda: kernels.causal_conv_silu(proj[:, Wd:], taps, state[:, Wd:], slot, activation="none", in_bias=xb,
+                                                    out_bias=cb, renew_state=spans is None))
+        note(f"rglru_conv_{n_rows}", ms, bytes_=n_rows * Wd * (2 + 4))
+        u = torch.randn(n_rows, Wd, device=dev)
+        ms = timed(lambda: kernels.rglru_gates(u, wa, wi, ba, bi, lam, 8.0))
+        note(f"rglru_gates_{n_rows}", ms, flops=4.0 * n_rows * Wd * bw, bytes_=n_rows * Wd * 12 + 2 * B * bw * bw * 2)
+        a, b = torch.rand(n_rows, Wd, device=dev), torch.randn(n_rows, Wd, device=dev)
+        ms = timed(lambda: kernels.rglru_scan(a, b, proj[:, :Wd], xb, state, spans, slot))
+        note(f"rglru_scan_{n_rows}", ms, bytes_=n_rows * Wd * (4 + 4 + 2 + 2))
+    Hd, dd = 16, 128
+    for n_rows, slot, spans in ((T, i32([0] * T), i32([[0, 0, T]])), (8, slots8, None)):
+        qkv = torch.randn(n_rows, 3 * Hd * dd, device=dev)
+        ab = torch.randn(n_rows, 2 * Hd, device=dev)
+        st = torch.zeros(9, Hd * kernels.scan_state_floats(dd, dd), device=dev)
+        A, dt = torch.randn(Hd, device=dev), torch.randn(Hd, device=dev)
+        ms = timed(lambda: kernels.delta_scan(qkv, (0, Hd * dd, 2 * Hd * dd), ab, (0, Hd), A, dt, st, spans, slot, Hd, Hd, dd,
+                                              dd, 1e-6))
+        note(f"delta_scan_{n_rows}", ms, bytes_=n_rows * 3 * Hd * dd * 4 + (2 * 8 * Hd * dd * dd * 4 if spans is None else 0))
+    # the router beside the other design's; the gated experts with and without a shared expert
+    E, top, eff = 16, 2, ffd // 2
+    for n_rows in (8, T):
+        z, corr = torch.randn(n_rows, E, device=dev), torch.randn(E, device=dev)
+        ms = timed(lambda: kernels.router_select(z, top, 4, 2, 2.5, sigmoid=True, correction=corr, group_top=2, normalize=True))
+        note(f"router_sigmoid_corrected_{n_rows}", ms)
+        ms = timed(lambda: kernels.router_select(z, top, 4, 2, 2.5))
+        note(f"router_softmax_all_{n_rows}", ms)
+
+    def experts_part(shared):
+        class Load:
+            def dtype(self, *a):
+                return torch.bfloat16
+
+            def __call__(self, n, out=None):
+                rows_ = eff // 2 if n.startswith("shared") else eff
+                shape = (E,) if n == "correction" else (E, width) if n == "router" else \
+                    ((width, rows_) if n.endswith("down") else (rows_, width))
+                t = bf(*shape) * 0.05
+                return t if out is None else out.copy_(t)
+        unit = dict(activation="swish", swish_alpha=1.702, gate_max=7.0, up_limit=7.0, up_shift=1.0)
+        params = dict(hidden_size=width, expert_size=eff, n_experts=E, top=top, expert="glu", **unit, scores="sigmoid",
+                      correction=True, groups=4, groups_kept=2, group_score="top2_sum", normalize=True, weight_scale=2.5)
+        if shared:
+            params["shared"] = dict(size=eff // 2, **unit)
+        return part_class("routed_experts")(params, Load(), Runtime(torch.bfloat16, torch.device(dev)))
+
+    zero = i32([0])
+    for shared, tag in ((True, "experts_with_shared"), (False, "experts_alone")):
+        part = experts_part(shared)
+        for n_rows in (1, 8, 64, T):
+            x = bf(n_rows, width)
+            ctx = StepContext(n_rows, zero, zero, zero)
+            ms = timed(lambda: part.step(x, ctx))
+            act = top * eff + (eff // 2 if shared else 0)
+            note(f"{tag}_{n_rows}_rows", ms, flops=6.0 * n_rows * act * width,
+                 bytes_=(min(E, n_rows * top) * eff + (eff // 2 if shared else 0)) * 3 * width * 2)
+        del part
+        torch.cuda.empty_cache()
+    kernels.check_bounded_waits(torch.device("cuda", 0))
+    print(json.dumps(out))
+    return 0
+
 
 def main() -> int:
     ap = argparse.ArgumentParser()
@@ -1017,12 +1257,12 @@ def main() -> int:
     ap.add_argument("--write-model", default=None, metavar="DIR",
                     help="with --impl reference: only write the model folder that arm uses (tied head, --layers of the 36) "
                          "to DIR and exit, for running baseline/_ref/bin/reference_runner by hand or under a profiler")
-    ap.add_argument("--study", default=None, choices=["prefill-clocks", "fivitar", "zogulorn", "dugopel"],
+    ap.add_argument("--study", default=None, choices=["prefill-clocks", "fivitar", "zogulorn", "dugopel", "kenovik"],
                     help="prefill-clocks: 40 prompt steps of 2,048 tokens back to back with the clock and the power "
                          "sampled every 20 ms; prints a table and no JSON line.  fivitar: prefill and decode of the "
                          "Fivitar design at two sizes of real layers beside Qwen3 at equal sizes, and the mixers' "
-                         "kernels alone; one JSON line of its own.  zogulorn, dugopel: the same for those designs (dugopel "
-                         "beside Fivitar's latent layers and Qwen3)")
+                         "kernels alone; one JSON line of its own.  zogulorn, dugopel, kenovik: the same for those "
+                         "designs (dugopel beside Fivitar's latent layers and Qwen3)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -1044,6 +1284,8 @@ def main() -> int:
         return study_zogulorn(args, peaks())
     if args.study == "dugopel":
         return study_dugopel(args, peaks())
+    if args.study == "kenovik":
+        return study_kenovik(args, peaks())
 
     import torch
     from garlic_inference_b200 import LanguageModel, Qwen3Config

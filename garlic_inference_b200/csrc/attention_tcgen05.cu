@@ -157,7 +157,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                              const int4* __restrict__ tiles, int n_q_tiles, bf16* __restrict__ out, int n_q, int n_kv,
                              int page_size, int max_pages, int n_pool_pages, int window, float scale_log2,
-                             int* __restrict__ error_flag, int chunk) {
+                             int* __restrict__ error_flag, int chunk, const float* __restrict__ sinks) {
     gi_pdl_start();
     extern __shared__ unsigned char ft_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)ft_raw + 1023) & ~(uintptr_t)1023);
@@ -412,7 +412,15 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (ok && !wait_warp(&ctl->o_done, (g0 + im.n_tiles - 1) & 1)) ok = false;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+            float inv = l > 0.f ? 1.f / l : 0.f;
+            if (sinks) {
+                // a score per head that joins the denominator without a value: against the larger of it and the
+                // row's reference, so that neither exponential overflows; O needs no pass of its own, its factor
+                // rides on the one division
+                const float s0 = sinks[im.h] * 1.4426950408889634f;
+                const float top = fmaxf(ref, s0), f = exp2f(ref - top);      // f = 0 for a row that saw no key
+                inv = f / (l * f + exp2f(s0 - top));
+            }
             bf16* dst = out + ((size_t)(im.row0 + r) * n_q + im.h) * FT_D;
 #pragma unroll
             for (int c4 = 0; c4 < FT_D / 32; ++c4) {
@@ -482,11 +490,12 @@ static int ft_make_map(CUtensorMap* map, const void* base, long long rows, long 
 
 // tiles: int32 [n_tiles, 4] = {slot, first q row, rows (<= 128), position of the first row}.
 // chunk > 0: a query sees only the keys of its own chunk of positions (chunks counted from position 0).
+// sinks: float32 [n_q] or null, a score per query head that joins the softmax's denominator without a value.
 // Takes head_dim 128 and page sizes that are a multiple of 64; everything else is refused.
 extern "C" int gi_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
                                             const int* tiles, int n_tiles, void* out, int n_tokens, int n_q, int n_kv,
                                             int d, int page_size, int max_pages, int n_pool_pages, int window,
-                                            int chunk, float scale, int* error_flag, void* stream) {
+                                            int chunk, float scale, int* error_flag, const float* sinks, void* stream) {
     GI_REQUIRE(chunk >= 0, "gi_attention_prefill_tcgen05: chunk %d", chunk);
     GI_REQUIRE(d == FT_D, "gi_attention_prefill_tcgen05: head_dim %d; this kernel takes 128", d);
     GI_REQUIRE(page_size > 0 && page_size % FT_BN == 0, "gi_attention_prefill_tcgen05: page size %d is no multiple of 64", page_size);
@@ -512,6 +521,6 @@ extern "C" int gi_attention_prefill_tcgen05(const void* q, const void* k_pool, c
     const long long grid = items < 2LL * n_sm ? items : 2LL * n_sm;      // two CTAs fit an SM
     gi_launch(flash_prefill_tcgen05_kernel, dim3((unsigned)grid), dim3(FT_THREADS), smem, (cudaStream_t)stream, map_q, map_k,
               map_v, block_table, (const int4*)tiles, n_tiles, (bf16*)out, n_q, n_kv, page_size, max_pages, n_pool_pages,
-              window, scale * 1.4426950408889634f, error_flag, chunk);
+              window, scale * 1.4426950408889634f, error_flag, chunk, sinks);
     return gi_check_launch("gi_attention_prefill_tcgen05");
 }

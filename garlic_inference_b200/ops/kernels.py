@@ -1222,11 +1222,12 @@ def tcgen05_attention_takes(dtype: torch.dtype, head_dim: int, page_size: int) -
 
 def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                               q_tiles128: torch.Tensor, scale: float, window: int, rows_covered: bool = False,
-                              chunk: int = 0) -> torch.Tensor:
+                              chunk: int = 0, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Flash attention of q [n, n_q, 128] over the paged cache on tcgen05 tensor cores (TMA-fed, S, P and
     P V in tensor memory).  `q_tiles128` int32 [n_tiles, 4] cuts the rows into runs of at most 128
     consecutive tokens of one sequence: {slot, first row, rows, position of the first row}.  `chunk` > 0: a query
-    sees only the keys of its own chunk of positions."""
+    sees only the keys of its own chunk of positions.  `sinks` float32 [n_q]: a score per head that joins the
+    softmax's denominator without a value."""
     l = require_gpu()
     _dense(q, "q", torch.bfloat16), _dense(k_pool, "k_pool", torch.bfloat16), _dense(v_pool, "v_pool", torch.bfloat16)
     _dense(block_table, "block_table", torch.int32), _dense(q_tiles128, "q_tiles128", torch.int32)
@@ -1237,11 +1238,12 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     if q_tiles128.dim() != 2 or q_tiles128.shape[1] != 4 or q_tiles128.data_ptr() % 16:
         raise KernelError("q_tiles128 must be int32 [n_tiles, 4] starting on 16 bytes")
     # rows in no tile (padding) stay zero; when the caller says that every row lies in a tile, nothing is filled
+    _check_sinks_bias(sinks, None, n_q)
     out = (torch.empty if rows_covered else torch.zeros)((n, n_q * d), dtype=q.dtype, device=q.device)
     check(l.gi_attention_prefill_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(q_tiles128),
                                          q_tiles128.shape[0], _ptr(out), n, n_q, n_kv, d, page_size,
                                          block_table.shape[1], n_pages, int(window or 0), int(chunk or 0), float(scale),
-                                         _ptr(tcgen05_error_flag(q.device)), _stream()), l)
+                                         _ptr(tcgen05_error_flag(q.device)), _ptr(sinks), _stream()), l)
     return out
 
 

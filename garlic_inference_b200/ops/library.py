@@ -69,7 +69,7 @@ _SIGNATURES = {
     "gi_attention_prefill_masked_bf16": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, I, F, P, P, I, P], I),
     "gi_attention_decode_masked_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P, I, P], I),
     "gi_attention_mma_takes": ([I, I], I),
-    "gi_attention_prefill_tcgen05": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, P, P], I),
+    "gi_attention_prefill_tcgen05": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, P, P, P], I),
     "gi_attention_decode_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P], I),
     "gi_set_pdl": ([I], None),
     "gi_attention_decode_tcgen05": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P], I),

@@ -178,7 +178,7 @@ class MaskedAttention(Mixer):
     def _run_rows(self, kv) -> int:
         """Height of the query runs of the prompt kernel that takes this mixer: 128 (tcgen05: one map, keys and
         values of 128, pages of a multiple of 64), 64 (mma.sync), 0 (the exact-order kernel, which needs none)."""
-        if self.maps == 1 and self.d == self.dv and self.sinks is None and self.dist_bias is None and \
+        if self.maps == 1 and self.d == self.dv and self.dist_bias is None and \
                 kernels.tcgen05_attention_takes(self.rt.dtype, self.d, kv.page_size):
             return 128
         return 64 if self._tensor_cores() else 0
@@ -240,7 +240,8 @@ class MaskedAttention(Mixer):
             covered = ctx.n_tokens == sum(ctx.seq_lens)
             if rows == 128:
                 att = kernels.attention_prefill_tcgen05(q, kv.k_pool, kv.v_pool, kv.block_table, runs, self.scale,
-                                                        self.window, rows_covered=covered, chunk=self.chunk)
+                                                        self.window, rows_covered=covered, chunk=self.chunk,
+                                                        sinks=self.sinks)
             else:
                 att = kernels.attention_prefill_masked_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, runs, self.scale,
                                                             window=self.window, chunk=self.chunk, maps=self.maps,

@@ -210,7 +210,8 @@ def _plain_attention(q, k, v, scale, sink, table_by_distance):
             s = s + table_by_distance[:, h].double()[dist]
         s = torch.where(torch.arange(T)[None, :] <= torch.arange(T)[:, None], s, torch.full_like(s, -math.inf))
         if sink is not None:
-            s = torch.cat([s, torch.full((T, 1), float(sink), dtype=torch.float64)], 1)
+            s0 = float(sink[h]) if isinstance(sink, (list, tuple)) else float(sink)
+            s = torch.cat([s, torch.full((T, 1), s0, dtype=torch.float64)], 1)
         p = torch.softmax(s, -1)[:, :T]
         out[:, h] = p @ v[:, g].double()
     return out
@@ -265,6 +266,27 @@ def test_attention_with_a_sink_and_a_far_key_that_stands_out(dtype):
                                                            n_splits=n_splits, sinks=sinks)
                 torch.testing.assert_close(one.cpu().double().view(4, H, dv), want[last.cpu()], **tol)
     assert int(status.item()) == 0
+
+
+def test_tcgen05_prompt_attention_with_sinks():
+    """The tcgen05 flash kernel (heads of 128, pages of 64) with a sink per head, among them one far above every score
+    and one far below: rows of three sequences, one of them continuing from cached keys."""
+    from garlic_inference_b200.ops import kernels
+    from garlic_inference_b200.parts import StepShape
+    from garlic_inference_b200.parts.attention import query_runs
+    torch.manual_seed(10)
+    H, G, d, page, T, scale = 4, 2, 128, 64, 333, 0.1
+    sink = [0.0, 30.0, -40.0, 1.5]
+    k, v, q = torch.randn(T, G, d).bfloat16(), torch.randn(T, G, d).bfloat16(), torch.randn(T, H, d).bfloat16()
+    want = _plain_attention(q.float(), k.float(), v.float(), scale, sink, None)
+    assert float(want[:, 1].abs().max()) < 1e-6 and float(want[0, 2].double().sub(v[0, 1].double()).abs().max()) < 1e-6
+    k_pool, v_pool, table = _paged(k.cuda(), v.cuda(), page)
+    # the last 133 rows as a step that continues a sequence of 200 cached tokens, runs of 128
+    runs = torch.from_numpy(query_runs(StepShape([1], [0], [133], [200], False), 128)).cuda()
+    got = kernels.attention_prefill_tcgen05(q[200:].contiguous().cuda(), k_pool, v_pool, table, runs, scale, 0, rows_covered=True,
+                                            sinks=torch.tensor(sink, device="cuda"))
+    torch.testing.assert_close(got.cpu().double().view(133, H, d), want[200:], rtol=3e-2, atol=3e-2)
+    kernels.check_bounded_waits(torch.device("cuda", 0))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
