@@ -81,7 +81,9 @@ struct AttnLayout {
     const float* sinks;
     const float* dist_bias;
     int n_dist;
+    int bias_smem;          // the prompt kernel keeps its head's column of dist_bias in shared memory (set by the launcher)
 };
+#define AT_BIAS_SMEM_MAX 8192      // distances up to which a head's biases are staged in shared memory
 #define AT_LOG2E 1.4426950408889634f
 
 // Element offset of row j of a sequence inside a pool (for key/value head kvh), or -1 when j is not below
@@ -239,6 +241,7 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
     bf16* sQ = reinterpret_cast<bf16*>(at_smem);
     bf16* sK = sQ + AT_BM * LD;
     bf16* sV = sK + 2 * AT_BN * LD;
+    float* sB = reinterpret_cast<float*>(sV + 2 * AT_BN * LDV);       // [n_dist] when lay.bias_smem: this head's biases, in powers of two
 
     const int4 ti = tiles[blockIdx.x];
     const int slot = ti.x, row0 = ti.y, n_rows = ti.z, pos0 = ti.w;
@@ -254,6 +257,8 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
     if (chunk > 0) lo = max(lo, pos0 / chunk * chunk);
     const int kt_lo = lo / AT_BN, n_tiles = hi / AT_BN - kt_lo + 1;
     const int n_kh = lay.n_kh > 0 ? lay.n_kh : n_kv, kh = kvh * lay.k_mul + lay.k_add;
+    if (lay.bias_smem)                           // read after the first barrier of the loop below
+        for (int i = threadIdx.x; i < lay.n_dist; i += AT_THREADS) sB[i] = __ldg(lay.dist_bias + (size_t)i * n_q + h) * AT_LOG2E;
 
     {   // the queries of the tile, rows beyond n_rows zero-filled
         constexpr int CH = D / 8;
@@ -310,7 +315,8 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
                     const bool ok = j <= p && (window <= 0 || j > p - window) && j >= c_row[e >> 1];
                     float sc = s[nt][e] * scale_log2;
                     if (lay.dist_bias && ok)
-                        sc = fmaf(__ldg(lay.dist_bias + (size_t)min(p - j, lay.n_dist - 1) * n_q + h), AT_LOG2E, sc);
+                        sc = lay.bias_smem ? sc + sB[min(p - j, lay.n_dist - 1)]
+                                           : fmaf(__ldg(lay.dist_bias + (size_t)min(p - j, lay.n_dist - 1) * n_q + h), AT_LOG2E, sc);
                     s[nt][e] = ok ? sc : -INFINITY;
                 }
             }
@@ -607,7 +613,7 @@ static AttnLayout plain_layout(int n_q, int d, int dv) {
     lay.q_ts = (long long)n_q * d; lay.q_hs = d; lay.q_o = 0;
     lay.o_ts = (long long)n_q * dv; lay.o_hs = dv; lay.o_o = 0;
     lay.n_kh = 0; lay.k_mul = 1; lay.k_add = 0; lay.chunk = 0; lay.maps = 1;
-    lay.sinks = lay.dist_bias = nullptr; lay.n_dist = 0;
+    lay.sinks = lay.dist_bias = nullptr; lay.n_dist = 0; lay.bias_smem = 0;
     return lay;
 }
 
@@ -617,7 +623,7 @@ static AttnLayout map_layout(int n_q, int n_kv, int d, int dv, int maps, int chu
     lay.q_ts = (long long)n_q * maps * d; lay.q_hs = (long long)maps * d; lay.q_o = 0;
     lay.o_ts = (long long)n_q * maps * dv; lay.o_hs = (long long)maps * dv; lay.o_o = 0;
     lay.n_kh = n_kv * maps; lay.k_mul = maps; lay.k_add = 0; lay.chunk = chunk; lay.maps = maps;
-    lay.sinks = lay.dist_bias = nullptr; lay.n_dist = 0;
+    lay.sinks = lay.dist_bias = nullptr; lay.n_dist = 0; lay.bias_smem = 0;
     return lay;
 }
 
@@ -630,9 +636,11 @@ static int prefill_bf16_layout(const void* q, const void* k_pool, const void* v_
     if (n_tiles == 0) return 0;
     const float scale_log2 = scale * 1.4426950408889634f;
     dim3 grid(n_tiles, n_q * lay.maps);
+    lay.bias_smem = lay.dist_bias && lay.n_dist <= AT_BIAS_SMEM_MAX;
 #define CALL(DK, DV)                                                                                           \
     {                                                                                                          \
-        const size_t smem = ((size_t)(AT_BM + 2 * AT_BN) * (DK + 8) + (size_t)2 * AT_BN * (DV + 8)) * sizeof(bf16); \
+        const size_t smem = ((size_t)(AT_BM + 2 * AT_BN) * (DK + 8) + (size_t)2 * AT_BN * (DV + 8)) * sizeof(bf16) + \
+                            (lay.bias_smem ? (size_t)lay.n_dist * sizeof(float) : 0);                          \
         if (int rc = set_smem((const void*)flash_prefill_kernel<DK, DV>, smem)) return rc;                     \
         gi_launch(flash_prefill_kernel<DK, DV>, grid, dim3(AT_THREADS), smem, (cudaStream_t)stream,            \
             (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, (const int4*)tiles,         \

@@ -131,6 +131,7 @@ rglru_gates_kernel(const float* __restrict__ u, const TW* __restrict__ wa_t, con
         for (int t = 0; t < RG_TG; ++t)
 #pragma unroll
             for (int j = 0; j < RG_OG; ++j) ra[t][j] = ri[t][j] = 0.f;
+#pragma unroll 2
         for (int k = ks; k < bw; k += RG_KS) {
             float wa4[4], wi4[4];
             rg_load4<TW>(w_s + (size_t)k * ws + oo, wa4);
@@ -299,9 +300,11 @@ extern "C" int gi_rglru_gates(const float* u, const void* wa_t, const void* wi_t
     }
     const int threads = RG_KS * (orange / RG_OG) * (tt / RG_TG);
     const int slices = (bw + orange - 1) / orange;
-    // many rows: the rows are cut over the grid's third axis until the GPU is full twice over
+    // many rows: the rows are cut over the grid's third axis until there are about eight blocks of threads to an SM
+    // one after the other (an SM holds one or two at a time; with fewer, longer ones the last round would leave most
+    // SMs idle, and a block's own copy of its weights costs little)
     const int tiles = (n_rows + tt - 1) / tt;
-    long long cut = (2LL * 148 + (long long)blocks * slices - 1) / ((long long)blocks * slices);
+    long long cut = (8LL * 148 + (long long)blocks * slices - 1) / ((long long)blocks * slices);
     cut = cut < 1 ? 1 : (cut > tiles ? tiles : (cut > 65535 ? 65535 : cut));
     const int rows_per_cta = (int)((tiles + cut - 1) / cut) * tt;
     dim3 grid(blocks, slices, (unsigned)((n_rows + rows_per_cta - 1) / rows_per_cta));

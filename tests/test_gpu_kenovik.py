@@ -415,7 +415,7 @@ def test_recurrent_unit_gates_scan_and_convolution_with_biases():
     the rest with the state carried in a slot's row, beside a second sequence and a padding row."""
     from garlic_inference_b200.ops import kernels
     torch.manual_seed(8)
-    for W, B, K in ((60, 5, 4), (48, 1, 1), (33, 3, 2), (256, 2, 3)):
+    for W, B, K in ((60, 5, 4), (48, 1, 1), (33, 3, 2), (256, 2, 3), (2048, 2, 2)):      # the last: blocks too wide for shared memory
         bw, T = W // B, 41
         m = {"width": W, "blocks": B, "conv": K}
         Wt = {"y": torch.zeros(W, 1), "y.b": torch.randn(W), "x": torch.zeros(W, 1), "x.b": torch.randn(W) * 0.3,
