@@ -1012,7 +1012,7 @@ def kenovik_config_dict(width, heads, ff, vocab, passes, head_dim=128, experts=1
     att2 = {"heads": heads, "kv_heads": kv, "dim": head_dim, "vdim": head_dim // 2, "scale": head_dim ** -0.5,
             "bias_max": 2048, "bias_rows": 64, "q_temp": {"coef": 0.1, "every": 512}}
     att = {"heads": heads, "kv_heads": kv, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
-           "rot": {"base": 1000000.0, "dims": head_dim // 2, "scaling": {"factor": 8.0}}}
+           "rot": {"base": 500000.0, "dims": head_dim // 2, "scaling": {"factor": 4.0}}}
     rec = {"width": width * 5 // 4, "blocks": max(1, width // 256), "conv": 4}
     eff = max(64, ff // top // 64 * 64)
     moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "shared": {"ff": eff // 2, "limit": 7.0},
@@ -1156,7 +1156,7 @@ def study_kenovik(args, pk) -> int:
             note(f"attention_decode_b8_tcgen05_{tag}_bare", ms, bytes_=by)
     # between projections and attention: biases + rotation of half of every head; projection norm + query factor;
     # and Qwen3's kernel (per-head norms, rotation by table)
-    freq = torch.tensor([1e6 ** (-2.0 * i / 64) / 8.0 for i in range(32)], dtype=torch.float32, device=dev)
+    freq = torch.tensor([5e5 ** (-2.0 * i / 64) / 4.0 for i in range(32)], dtype=torch.float32, device=dev)
     cols = (H + 2 * G) * d
     bias, wn = torch.randn(cols, device=dev), torch.randn((H + G) * d, device=dev)
     kp, vp = bf(8 * T // page, G, page, d), bf(8 * T // page, G, page, d)
