@@ -321,10 +321,22 @@ extern "C" int gi_rglru_gates(const float* u, const void* wa_t, const void* wi_t
     return gi_check_launch("gi_rglru_gates");
 }
 
+// The gate branch's activation, the tanh form of gelu: with the library's tanh for a float32 engine; for bfloat16
+// (the activation of a projection, whose result is rounded to 8 bits of mantissa right after) with the hardware's
+// approximate tanh, which is good to about 11 bits.
+template <typename T> __device__ __forceinline__ float rg_gate_act(float z) { return rg_gelu_tanh(z); }
+template <> __device__ __forceinline__ float rg_gate_act<bf16>(float z) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return 0.5f * z * (1.f + t);
+}
+
 // spans [n_seq, 3] = {slot, first row, rows}, or null: every row is a sequence of its own with the slot of tok_slot.
-#define RG_AHEAD 16          // tokens whose inputs a thread asks for before it walks them
+#define RG_SUB 4             // tokens to a group of the scan's ring of inputs
+#define RG_DEPTH 8           // groups in the ring: 32 tokens' inputs under way
+#define RG_SCAN_THREADS 32    // one warp to a block: one long prompt of a few thousand channels then reaches every SM
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(RG_SCAN_THREADS)
 rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ b, const T* __restrict__ y, long long ldy,
                   const void* __restrict__ y_bias, int bias_dtype, float* __restrict__ state, long long state_stride,
                   const int* __restrict__ spans, const int* __restrict__ tok_slot, T* __restrict__ out, long long ldo,
@@ -341,31 +353,53 @@ rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ b, cons
     }
     const float yb = y_bias ? load_w(y_bias, bias_dtype, c) : 0.f;
     float S = state[(size_t)slot * state_stride + c];
-    // the next tokens' inputs are asked for before the present ones are walked, so that the chain of dependent
-    // multiply-adds never waits for memory
-    float av[RG_AHEAD], bv[RG_AHEAD], yv[RG_AHEAD];
-    auto fetch = [&](int t0, float (&fa)[RG_AHEAD], float (&fb)[RG_AHEAD], float (&fy)[RG_AHEAD]) {
+    if (len == 1) {                                          // a decode step's row: nothing to run ahead of
+        const size_t r = (size_t)start;
+        S = fmaf(a[r * width + c], S, b[r * width + c]);
+        out[r * ldo + c] = from_f32<T>(S * rg_gate_act<T>(to_f32(y[r * ldy + c]) + yb));
+        state[(size_t)slot * state_stride + c] = S;
+        return;
+    }
+    // The inputs of the next 32 tokens are on their way while a token is walked: a ring of eight groups of four
+    // tokens in registers, each refilled right after it was used; beyond that the lines of the 32 tokens after
+    // those are asked into L2 (a hint: lane j names token j of them).  A group is walked in two passes: the chain of
+    // dependent multiply-adds alone, then the gate branch's activation and the products, which wait for nothing.
+    const int lane = threadIdx.x & 31;
+    const size_t cw = (size_t)(c - lane);                    // the warp's first channel
+    float ra[RG_DEPTH][RG_SUB], rb[RG_DEPTH][RG_SUB], ry[RG_DEPTH][RG_SUB];
+    auto fetch = [&](int t0, float (&fa)[RG_SUB], float (&fb)[RG_SUB], float (&fy)[RG_SUB]) {
 #pragma unroll
-        for (int j = 0; j < RG_AHEAD; ++j) {
+        for (int j = 0; j < RG_SUB; ++j) {
             const bool in = t0 + j < len;
             const size_t r = (size_t)(start + (in ? t0 + j : 0));
-            fa[j] = in ? a[r * width + c] : 1.f;
+            fa[j] = in ? a[r * width + c] : 1.f;             // beyond the sequence: S stays as it is
             fb[j] = in ? b[r * width + c] : 0.f;
             fy[j] = in ? to_f32(y[r * ldy + c]) : 0.f;
         }
     };
-    fetch(0, av, bv, yv);
-    for (int t0 = 0; t0 < len; t0 += RG_AHEAD) {
-        float an[RG_AHEAD], bn[RG_AHEAD], yn[RG_AHEAD];
-        fetch(t0 + RG_AHEAD, an, bn, yn);
 #pragma unroll
-        for (int j = 0; j < RG_AHEAD; ++j) {
-            if (t0 + j >= len) break;
-            S = fmaf(av[j], S, bv[j]);
-            out[(size_t)(start + t0 + j) * ldo + c] = from_f32<T>(S * rg_gelu_tanh(yv[j] + yb));
+    for (int d = 0; d < RG_DEPTH; ++d) fetch(d * RG_SUB, ra[d], rb[d], ry[d]);
+    for (int t0 = 0; t0 < len; t0 += RG_DEPTH * RG_SUB) {
+        if (t0 + 2 * RG_DEPTH * RG_SUB + lane < len) {
+            const size_t r = (size_t)(start + t0 + 2 * RG_DEPTH * RG_SUB + lane);
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(a + r * width + cw));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(b + r * width + cw));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(y + r * ldy + cw));
         }
 #pragma unroll
-        for (int j = 0; j < RG_AHEAD; ++j) { av[j] = an[j]; bv[j] = bn[j]; yv[j] = yn[j]; }
+        for (int d = 0; d < RG_DEPTH; ++d) {
+            const int t1 = t0 + d * RG_SUB;
+            float sv[RG_SUB];
+#pragma unroll
+            for (int j = 0; j < RG_SUB; ++j) {
+                S = fmaf(ra[d][j], S, rb[d][j]);
+                sv[j] = S;
+            }
+#pragma unroll
+            for (int j = 0; j < RG_SUB; ++j)
+                if (t1 + j < len) out[(size_t)(start + t1 + j) * ldo + c] = from_f32<T>(sv[j] * rg_gate_act<T>(ry[d][j] + yb));
+            fetch(t1 + RG_DEPTH * RG_SUB, ra[d], rb[d], ry[d]);
+        }
     }
     state[(size_t)slot * state_stride + c] = S;
 }
@@ -374,15 +408,15 @@ extern "C" int gi_rglru_scan(const float* a, const float* b, const void* y, long
                              int bias_dtype, float* state, long long state_stride, const int* spans, const int* tok_slot,
                              void* out, long long ldo, int n_seqs, int width, void* stream) {
     GI_REQUIRE(n_seqs >= 0 && width > 0 && ldy >= width && ldo >= width && state_stride >= width, "gi_rglru_scan: sizes");
-    GI_REQUIRE((width + 127) / 128 <= 65535, "gi_rglru_scan: %d channels", width);
+    GI_REQUIRE((width + RG_SCAN_THREADS - 1) / RG_SCAN_THREADS <= 65535, "gi_rglru_scan: %d channels", width);
     if (n_seqs == 0) return 0;
-    dim3 grid(n_seqs, (width + 127) / 128);
+    dim3 grid(n_seqs, (width + RG_SCAN_THREADS - 1) / RG_SCAN_THREADS);
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32)
-        gi_launch(rglru_scan_kernel<float>, grid, dim3(128), 0, s, a, b, (const float*)y, ldy, y_bias, bias_dtype, state,
+        gi_launch(rglru_scan_kernel<float>, grid, dim3(RG_SCAN_THREADS), 0, s, a, b, (const float*)y, ldy, y_bias, bias_dtype, state,
                   state_stride, spans, tok_slot, (float*)out, ldo, width);
     else if (act_dtype == GI_DTYPE_BF16)
-        gi_launch(rglru_scan_kernel<bf16>, grid, dim3(128), 0, s, a, b, (const bf16*)y, ldy, y_bias, bias_dtype, state,
+        gi_launch(rglru_scan_kernel<bf16>, grid, dim3(RG_SCAN_THREADS), 0, s, a, b, (const bf16*)y, ldy, y_bias, bias_dtype, state,
                   state_stride, spans, tok_slot, (bf16*)out, ldo, width);
     else
         GI_REQUIRE(false, "gi_rglru_scan: activation dtype %d", act_dtype);

@@ -423,11 +423,8 @@ def test_recurrent_unit_gates_scan_and_convolution_with_biases():
               "ra.b": torch.randn(B, bw), "ri": torch.randn(B, bw, bw) * 0.4, "ri.b": torch.randn(B, bw),
               "lam": torch.randn(W) * 2, "o": torch.eye(W)}
         xin, yin = torch.randn(T, W), torch.randn(T, W)
-
-        class Feed(dict):                      # the plain block with the two projections' results given
-            pass
         Wp = dict(Wt)
-        # y = Wy h + by with h = [yin | xin] picked by identity-like matrices
+        # the plain block with the two projections' results given: h = [yin | xin], picked by identity-like matrices
         h = torch.cat([yin, xin], 1)
         Wp["y"] = torch.cat([torch.eye(W), torch.zeros(W, W)], 1)
         Wp["x"] = torch.cat([torch.zeros(W, W), torch.eye(W)], 1)
