@@ -121,7 +121,8 @@ def attention_bias(h, W, m, positions, eps):
     rel = W["rel"]                                                         # [rows, heads]
     rows = rel.shape[0]
     dist = (positions[:, None] - positions[None, :]).clamp(min=0)
-    buckets = torch.tensor([[distance_bucket(int(n), rows, m["bias_max"]) for n in row] for row in dist.tolist()])
+    by_distance = torch.tensor([distance_bucket(n, rows, m["bias_max"]) for n in range(int(dist.max()) + 1)])
+    buckets = by_distance[dist]
     seen = positions[None, :] <= positions[:, None]
     out = torch.zeros(T, H, dv, dtype=h.dtype)
     for n in range(H):

@@ -75,6 +75,24 @@ def test_tensor_core_kernels_on_pages_of_64(model, folder):
         tk.judge_routed(got, want, own, "bfloat16", "tc on pages of 64", folder("tc"), reqs)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_of_a_thousand_tokens_through_the_trace_program(dtype, folder, tmp_path):
+    """Requests of 1,100, 425, 97 and 1 tokens through bin/trace_run on its default pages of 64: whole, and started
+    together with their last 40 % decoded together.  Far keys among a thousand, distances beyond every bias table, the
+    query's factor after eight steps, a state carried a thousand tokens."""
+    reqs = _requests("long", [1100, 425, 97, 1], seed=17)
+    want, own = tk.plain_pair(folder("long"), reqs)
+    steps = tiny.trace_whole(reqs) + [dict(s, step=s["step"] + 4, entries=[dict(e, id=e["id"] + "b") for e in s["entries"]],
+                                           end=[r + "b" for r in s["end"]])
+                                      for s in tiny.trace_batched(reqs, [list(reqs)], prompt_frac=0.6)]
+    got = tiny.run_trace_program(folder("long"), dtype, steps, tmp_path / "out", 2048, tk.TINY["long"]["vocab"])
+    first = {rid: rows for rid, rows in got.items() if not rid.endswith("b")}
+    second = {rid[:-1]: rows for rid, rows in got.items() if rid.endswith("b")}
+    for part, what in ((first, "whole"), (second, "together")):
+        tiny.assert_covers(part, reqs)
+        tk.judge_routed(part, want, own, dtype, f"long {dtype} {what}", folder("long"), reqs)
+
+
 def test_float32_logits_do_not_depend_on_the_cut_or_the_batch(model):
     """Without routed experts (whose few-row and many-row paths sum in different orders) the same position gives
     the same bits whole, in portions, decoded, alone or in a batch: attention in the exact-order kernel, the

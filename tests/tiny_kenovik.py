@@ -83,6 +83,14 @@ TINY = {
                        _with(_sink(2, 2, 128, 128, dims=128, base=50000.0)),
                        _with(_bias(34, 2, 16, 16, rows=12, far=70), _dense(64)),
                        _with(_bias(3, 3, 32, 16, rows=32, far=500, temp=(1.0, 7)))]),
+    # prompts of a thousand tokens on pages of 64: every attention on its tensor-core kernels (flash on tcgen05 for the
+    # heads of 128, mma.sync for the others), distances far beyond the bias tables' reach, three layers passed twice
+    "long": dict(vocab=384, width=192, eps=1e-5, emb=2.0, seed=50, std=0.06, norm_std=0.1, loop=(1, 4, 2),
+                 layers=[_with(_rglru(240, 4, 3), _moe(48, 1.5, 12, 4, 1.8, groups=(3, 2), shared=(80, 2.5))),
+                         _with(_sink(6, 3, 32, 64, dims=16, base=250000.0, factor=2.0), _dense(256)),
+                         _with(_bias(4, 2, 64, 64, rows=20, far=300, temp=(0.25, 128)), _moe(40, 1.0, 8, 2, 2.2, groups=(4, 3))),
+                         _with(_bias(5, 1, 48, 24, rows=32, far=900), _dense(160)),
+                         _with(_sink(2, 1, 128, 128, dims=64, base=10000.0), _moe(32, 3.0, 6, 3, 1.0, shared=(64, 1.0)))]),
     # sizes that are multiples of nothing the kernels like
     "odd": dict(vocab=263, width=50, eps=1e-5, emb=2.5, seed=48, std=0.1, norm_std=0.1, loop=(1, 2, 2),
                 layers=[_with(_sink(3, 3, 6, 10, dims=2, base=40.0, factor=1.5), _moe(18, 1.5, 6, 2, 1.3, groups=(2, 1))),
